@@ -1,0 +1,127 @@
+// extern "C" surface of libb200gpt (declared in include/b200_gpt.h): argument checks and
+// composition of the kernels; no kernel code lives here.
+#include "common.cuh"
+
+namespace {
+thread_local cudaError_t g_last_cuda = cudaSuccess;
+int note(int st) {
+  if (st == B200_ERR_CUDA) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) g_last_cuda = e;
+  }
+  return st;
+}
+bool valid_dtype(int dt) { return dt == B200_F32 || dt == B200_F16 || dt == B200_BF16; }
+size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+bool direct_operand_ok(int dtype, int64_t K) { return dtype != B200_F32 && K % 8 == 0; }
+}  // namespace
+
+extern "C" {
+
+const char* b200_status_string(int status) {
+  switch (status) {
+    case B200_OK: return "ok";
+    case B200_ERR_BAD_ARGUMENT: return "bad argument";
+    case B200_ERR_ALIGNMENT: return "alignment rule violated";
+    case B200_ERR_CUDA: return "CUDA call failed";
+    case B200_ERR_UNSUPPORTED: return "not supported";
+    case B200_ERR_WORKSPACE: return "workspace missing or too small";
+    case B200_ERR_DEVICE_WAIT: return "a kernel abandoned a bounded wait";
+  }
+  return "unknown status";
+}
+
+const char* b200_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
+
+int b200_abi_version(void) { return 1; }
+
+int b200_embedding(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t B, int64_t L, int64_t V,
+                   int64_t P, int64_t H, int dtype, int* bad_id_flag, void* stream) {
+  if (B < 0 || L < 0 || V < 1 || P < 1 || H < 0 || !valid_dtype(dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (L > P) return B200_ERR_BAD_ARGUMENT;
+  if (B * L == 0 || H == 0) return B200_OK;
+  if (!ids || !wte || !wpe || !out) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, (cudaStream_t)stream));
+}
+
+int b200_layernorm(const void* x, const void* w, const void* b, void* out, int64_t M, int64_t H, float eps,
+                   int in_dtype, int out_dtype, void* stream) {
+  if (M < 0 || H < 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (M == 0 || H == 0) return B200_OK;
+  if (!x || !w || !b || !out) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_layernorm(x, w, b, out, M, H, eps, in_dtype, out_dtype, (cudaStream_t)stream));
+}
+
+int b200_pack_operand(const void* src, void* dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst,
+                      int transpose, int src_dtype, int dst_dtype, void* stream) {
+  if (rows < 0 || cols < 0 || !valid_dtype(src_dtype) || dst_dtype == B200_F32 || !valid_dtype(dst_dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!src || !dst || ld_src < cols || ld_dst < (transpose ? rows : cols)) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_pack(src, dst, rows, cols, ld_src, ld_dst, transpose, src_dtype, dst_dtype, (cudaStream_t)stream));
+}
+
+int b200_gemm(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+              int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
+              int add_gelu, int* status_word, void* stream) {
+  if (!valid_dtype(io_dtype)) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_gemm(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, io_dtype, add_gelu,
+                                status_word, (cudaStream_t)stream));
+}
+
+size_t b200_ffn_workspace_bytes(int64_t M, int64_t N, int64_t K, int w_is_nk, int dtype) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const size_t kp = (size_t)((K + 7) / 8 * 8);
+  size_t bytes = 0;
+  if (!direct_operand_ok(dtype, K)) bytes += round256((size_t)M * kp * 2);
+  if (!(w_is_nk && direct_operand_ok(dtype, K))) bytes += round256((size_t)N * kp * 2);
+  return bytes;
+}
+
+int b200_ffn(const void* x, const void* w, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+             int64_t K, int64_t ld_out, int w_is_nk, int add_gelu, int dtype, void* workspace, size_t workspace_bytes,
+             int* status_word, void* stream) {
+  if (!valid_dtype(dtype) || M < 0 || N < 0 || K < 0) return B200_ERR_BAD_ARGUMENT;
+  if (M == 0 || N == 0) return B200_OK;
+  if (K == 0 || !x || !w || !out || ld_out < N) return B200_ERR_BAD_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int op_dtype = dtype == B200_BF16 ? B200_BF16 : B200_F16;
+  const int64_t kp = (K + 7) / 8 * 8;
+  const bool x_direct = direct_operand_ok(dtype, K) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  const bool w_direct = w_is_nk && direct_operand_ok(dtype, K) && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  size_t need = 0;
+  if (!x_direct) need += round256((size_t)M * kp * 2);
+  if (!w_direct) need += round256((size_t)N * kp * 2);
+  if (need > 0 && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))) return B200_ERR_WORKSPACE;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  const void* a = x;
+  const void* b = w;
+  int64_t lda = K, ldb = K;
+  if (!x_direct) {
+    int st = note(b200::launch_pack(x, ws, M, K, K, kp, 0, dtype, op_dtype, s));
+    if (st != B200_OK) return st;
+    a = ws;
+    lda = kp;
+    ws += round256((size_t)M * kp * 2);
+  }
+  if (!w_direct) {
+    int st = w_is_nk ? note(b200::launch_pack(w, ws, N, K, K, kp, 0, dtype, op_dtype, s))
+                     : note(b200::launch_pack(w, ws, K, N, N, kp, 1, dtype, op_dtype, s));
+    if (st != B200_OK) return st;
+    b = ws;
+    ldb = kp;
+  }
+  return note(b200::launch_gemm(a, b, bias, residual, out, M, N, K, lda, ldb, N, ld_out, op_dtype, dtype, add_gelu, status_word, s));
+}
+
+int b200_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L, int64_t D,
+                   const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                   const int64_t o_strides[3], float scale, int in_dtype, int out_dtype, void* stream) {
+  if (B < 0 || NH < 0 || L < 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256) return B200_ERR_BAD_ARGUMENT;
+  if (B == 0 || NH == 0 || L == 0) return B200_OK;
+  if (!q || !k || !v || !out || !q_strides || !k_strides || !v_strides || !o_strides) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_attention(q, k, v, out, B, NH, L, D, q_strides, k_strides, v_strides, o_strides, scale, in_dtype,
+                                     out_dtype, (cudaStream_t)stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,142 @@
+// Shared definitions for the sm_100a kernels of the GPT-2 forward path.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200_gpt.h"
+
+namespace b200 {
+
+// ------------------------------------------------------------------ dtype helpers
+template <typename T>
+struct DType;
+template <>
+struct DType<float> {
+  static constexpr int code = B200_F32;
+};
+template <>
+struct DType<__half> {
+  static constexpr int code = B200_F16;
+};
+template <>
+struct DType<__nv_bfloat16> {
+  static constexpr int code = B200_BF16;
+};
+
+__host__ __device__ inline int dtype_size(int dt) { return dt == B200_F32 ? 4 : 2; }
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// 8 consecutive elements <-> 8 floats.  The vector forms need 16-byte alignment.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&f)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__half>(__half* p, const float (&f)[8]) {
+  uint4 u;
+  __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// tanh-form GELU with tanh(y) = 2*sigmoid(2y) - 1, the formulation the reference
+// kernel evaluates (kernels.py:15-26 of the reference project).
+__device__ __forceinline__ float gelu_new(float x) {
+  const float a = 0.7978845608028654f;  // sqrt(2/pi)
+  float b = x + 0.044715f * x * x * x;
+  float y = a * b;
+  float s = 1.0f / (1.0f + __expf(-2.0f * y));
+  float t = 2.0f * s - 1.0f;
+  return 0.5f * x * (1.0f + t);
+}
+
+// ------------------------------------------------------------------ launch helpers
+inline int status_from_cuda(cudaError_t e) { return e == cudaSuccess ? B200_OK : B200_ERR_CUDA; }
+
+int sm_count();  // cached multiprocessor count of the current device
+
+// ------------------------------------------------------------------ internal launchers
+int launch_embedding(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t T, int64_t L, int64_t V,
+                     int64_t P, int64_t H, int dtype, int* bad_id_flag, cudaStream_t stream);
+int launch_layernorm(const void* x, const void* w, const void* b, void* out, int64_t M, int64_t H, float eps,
+                     int in_dtype, int out_dtype, cudaStream_t stream);
+int launch_pack(const void* src, void* dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst, int transpose,
+                int src_dtype, int dst_dtype, cudaStream_t stream);
+int launch_gemm(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
+                int add_gelu, int* status_word, cudaStream_t stream);
+int launch_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L,
+                     int64_t D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                     const int64_t* o_strides, float scale, int in_dtype, int out_dtype, cudaStream_t stream);
+
+}  // namespace b200

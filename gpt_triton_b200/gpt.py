@@ -1,0 +1,242 @@
+"""GPT-2 forward modules on top of the sm_100a operators, with the reference's module surface.
+
+Class names, constructor arguments, parameter names and therefore the state-dict layout are
+those of the reference (``FusedAttention`` gpt.py:21-67, ``FusedMLP`` gpt.py:70-119,
+``GPTConfig`` gpt.py:122-129, ``FusedGPT`` gpt.py:132-196), so a converted Hugging Face GPT-2
+state dict loads unchanged (gpt.py:199-247).  What is new:
+
+* ``FusedGPT.forward`` still returns the final hidden state (gpt.py:180); ``FusedGPT.logits`` /
+  ``FusedGPT.lm_head`` add the tied head that the reference leaves commented out
+  (gpt.py:159-161, 172-179) and use ``wte`` itself as a K-major operand, not its transpose;
+* every GEMM weight is packed once per parameter version into the tensor-core operand layout;
+* attention reads q/k/v as views of the c_attn output and writes merged heads, so the four
+  per-layer copies of the reference (kernels.py:359-365, gpt.py:51) do not exist;
+* ``GPU_TO_FLOPS`` has a ``"b200"`` entry, and ``executed_fwd_flops`` counts what the tensor
+  cores really execute.
+
+Forward/eval only: in the reference the training branch cannot run either (gpt.py:165 reads a
+config field that gpt.py:129 does not define).
+"""
+
+from dataclasses import dataclass
+
+import torch
+from torch import nn
+
+from . import kernels as K
+
+GPU_TO_FLOPS = {"v100": 130e12, "a100": 312e12, "h100": 989e12, "b200": 2250e12}
+GPU_TO_FLOPS = {k: int(v) for k, v in GPU_TO_FLOPS.items()}
+
+
+def _uniform(*shape):
+    # the reference initialises every matrix and bias with torch.rand; real use loads a state dict
+    return nn.Parameter(torch.rand(*shape))
+
+
+def _ln_params(module, h):
+    module.layer_norm_weight = nn.Parameter(torch.ones(h))
+    module.layer_norm_bias = nn.Parameter(torch.zeros(h))
+
+
+def _linear_flops(tokens, fan_in, fan_out):
+    """Multiply-adds plus the bias add, the way the reference counts a projection."""
+    return tokens * fan_out * 2 * fan_in + tokens * fan_out
+
+
+def _ln_flops(tokens, h):
+    return 2 * tokens * h
+
+
+class _OperandCache:
+    """PackedWeight per parameter; rebuilt when the parameter is replaced, cast, moved or
+    written in place (torch bumps ``_version`` on in-place writes)."""
+
+    def __init__(self):
+        self._slots = {}
+
+    def __call__(self, param, weight_is_nk=False):
+        t = param.data
+        tag = (t.data_ptr(), t._version, t.dtype, t.device, tuple(t.shape))
+        slot = self._slots.get(id(param))
+        if slot is None or slot[0] != tag:
+            slot = (tag, K.pack_weight(t.contiguous(), weight_is_nk=weight_is_nk))
+            self._slots[id(param)] = slot
+        return slot[1]
+
+
+class _EvalOnly(nn.Module):
+    def _check_eval(self):
+        if self.training:
+            raise NotImplementedError("libb200gpt implements the forward/eval path only: call .eval() first")
+
+
+class FusedAttention(_EvalOnly):
+    def __init__(self, hidden_size, num_heads, dropout_prob=0.0):
+        super().__init__()
+        self.hidden_size, self.num_heads, self.dropout_prob = hidden_size, num_heads, dropout_prob
+        _ln_params(self, hidden_size)
+        self.c_attn_weight = _uniform(hidden_size, 3 * hidden_size)
+        self.c_attn_bias = _uniform(3 * hidden_size)
+        self.c_proj_weight = _uniform(hidden_size, hidden_size)
+        self.c_proj_bias = _uniform(hidden_size)
+        self._operand = _OperandCache()
+
+    def forward(self, x):
+        self._check_eval()
+        skip = x
+        y = K.fused_layer_norm(x, self.layer_norm_weight.data, self.layer_norm_bias.data)
+        q, k, v = K.matmul_and_split_qkv(y, self._operand(self.c_attn_weight), self.c_attn_bias.data, self.num_heads)
+        y = K.flash_attention_v1(q, k, v, merged_heads=True).view(skip.shape)
+        return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=skip)
+
+    def get_fwd_flops(self, num_tokens):
+        h = self.hidden_size
+        return _ln_flops(num_tokens, h) + _linear_flops(num_tokens, h, 3 * h) + _linear_flops(num_tokens, h, h)
+
+
+class FusedMLP(_EvalOnly):
+    def __init__(self, hidden_size, dropout_prob=0.0):
+        super().__init__()
+        self.hidden_size, self.intermediate_size, self.dropout_prob = hidden_size, 4 * hidden_size, dropout_prob
+        _ln_params(self, hidden_size)
+        self.ffn1_weight = _uniform(hidden_size, self.intermediate_size)
+        self.ffn1_bias = _uniform(self.intermediate_size)
+        self.ffn2_weight = _uniform(self.intermediate_size, hidden_size)
+        self.ffn2_bias = _uniform(hidden_size)
+        self._operand = _OperandCache()
+
+    def forward(self, x):
+        self._check_eval()
+        y = K.fused_layer_norm(x, self.layer_norm_weight.data, self.layer_norm_bias.data)
+        y = K.fused_ffn(y, self._operand(self.ffn1_weight), bias=self.ffn1_bias.data, add_gelu=True)
+        return K.fused_ffn(y, self._operand(self.ffn2_weight), bias=self.ffn2_bias.data, residual=x)
+
+    def get_fwd_flops(self, num_tokens):
+        h, mid = self.hidden_size, self.intermediate_size
+        return _ln_flops(num_tokens, h) + _linear_flops(num_tokens, h, mid) + _linear_flops(num_tokens, mid, h)
+
+
+@dataclass
+class GPTConfig:
+    vocab_size: int = 50304
+    block_size: int = 512
+    n_layer: int = 12
+    n_head: int = 12
+    n_embd: int = 768
+    dropout: float = 0.1
+
+
+class FusedGPT(_EvalOnly):
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        h = config.n_embd
+        self.wte_weight = _uniform(config.vocab_size, h)
+        self.wpe_weight = _uniform(config.block_size, h)
+        layers = []
+        for _ in range(config.n_layer):
+            layers.append(nn.Sequential(FusedAttention(h, config.n_head, dropout_prob=config.dropout),
+                                        FusedMLP(h, dropout_prob=config.dropout)))
+        self.blocks = nn.ModuleList(layers)
+        _ln_params(self, h)
+        self._operand = _OperandCache()
+
+    def forward(self, x):
+        """ids (batch, seqlen) -> final hidden state (batch, seqlen, n_embd)."""
+        self._check_eval()
+        y = K.fused_embeddings(x, self.wte_weight.data, self.wpe_weight.data)
+        for attention, mlp in self.blocks:
+            y = mlp(attention(y))
+        return K.fused_layer_norm(y, self.layer_norm_weight.data, self.layer_norm_bias.data)
+
+    @torch.no_grad()
+    def lm_head(self, hidden):
+        """hidden (batch, seqlen, n_embd) -> logits (batch, seqlen, vocab_size) with the tied
+        embedding matrix.  The logits buffer's row pitch is padded to a multiple of 8 elements so
+        every row starts 16-byte aligned; the result is the [..., :vocab_size] view of it."""
+        B, L, h = hidden.shape
+        V = self.config.vocab_size
+        pitch = (V + 7) // 8 * 8
+        buf = torch.empty((B * L, pitch), device=hidden.device, dtype=hidden.dtype)
+        K.fused_ffn(hidden.reshape(B * L, h), self._operand(self.wte_weight, weight_is_nk=True), out=buf[:, :V])
+        return buf.view(B, L, pitch)[:, :, :V]
+
+    @torch.no_grad()
+    def logits(self, x):
+        """ids -> logits: forward() followed by the tied lm_head."""
+        return self.lm_head(self.forward(x))
+
+    def get_fwd_flops(self, num_tokens):
+        """The reference's analytic count (gpt.py:182-196): embeddings counted as matmuls,
+        attention score/value products not counted."""
+        c = self.config
+        total = sum(m.get_fwd_flops(num_tokens) for pair in self.blocks for m in pair)
+        total += _ln_flops(num_tokens, c.n_embd)
+        total += num_tokens * c.n_embd * 2 * (c.vocab_size + c.block_size)
+        return total
+
+
+def executed_fwd_flops(config, batch, seqlen, with_lm_head=True):
+    """Tensor-core flop one forward really executes: the four projections of every layer,
+    causal attention (QK^T and PV over the lower triangle) and optionally the tied lm_head."""
+    T, h, d = batch * seqlen, config.n_embd, config.n_embd // config.n_head
+    gemm = 2 * T * 12 * h * h * config.n_layer
+    attn = 4 * batch * config.n_head * d * (seqlen * (seqlen + 1) // 2) * config.n_layer
+    head = 2 * T * h * config.vocab_size if with_lm_head else 0
+    return gemm + attn + head
+
+
+_HF_TOP = {"wte.weight": "wte_weight", "wpe.weight": "wpe_weight", "ln_f.weight": "layer_norm_weight", "ln_f.bias": "layer_norm_bias"}
+# (HF sub-key, slot in the nn.Sequential pair, our parameter stem)
+_HF_BLOCK = [("ln_1", 0, "layer_norm"), ("attn.c_attn", 0, "c_attn"), ("attn.c_proj", 0, "c_proj"),
+             ("ln_2", 1, "layer_norm"), ("mlp.c_fc", 1, "ffn1"), ("mlp.c_proj", 1, "ffn2")]
+_HF_DROPPED = ("attn.bias", "attn.masked_bias")  # causal-mask buffers of older HF versions
+
+
+def convert_huggingface_to_triton(hf_sd, hf_config):
+    """Hugging Face ``GPT2Model`` state dict -> (``FusedGPT`` state dict, ``GPTConfig``).
+
+    Pure key renaming as in gpt.py:199-237 (HF Conv1D weights are already [in, out]); mask
+    buffers are dropped; ``n_positions`` stands in when the config carries no ``n_ctx``."""
+    config = GPTConfig(vocab_size=hf_config.vocab_size, block_size=getattr(hf_config, "n_ctx", None) or hf_config.n_positions,
+                       n_layer=hf_config.n_layer, n_head=hf_config.n_head, n_embd=hf_config.n_embd, dropout=0.1)
+    rename = dict(_HF_TOP)
+    for i in range(config.n_layer):
+        for hf_stem, slot, stem in _HF_BLOCK:
+            for kind in ("weight", "bias"):
+                rename[f"h.{i}.{hf_stem}.{kind}"] = f"blocks.{i}.{slot}.{stem}_{kind}"
+        for dropped in _HF_DROPPED:
+            rename[f"h.{i}.{dropped}"] = None
+    out = {}
+    for name, tensor in hf_sd.items():
+        target = rename[name]  # KeyError on an unknown key, like the reference
+        if target is not None:
+            out[target] = tensor
+    return out, config
+
+
+def convert_hf_and_load_model(model_id, device):
+    """As gpt.py:240-247; needs the Hugging Face checkpoint to be reachable."""
+    from transformers import GPT2Model
+
+    hf_model = GPT2Model.from_pretrained(model_id)
+    state_dict, config = convert_huggingface_to_triton(hf_model.state_dict(), hf_model.config)
+    model = FusedGPT(config)
+    model.load_state_dict(state_dict)
+    return model.to(device).eval(), hf_model.to(device).eval()
+
+
+def estimate_days(flops, mfu=0.45, gpu="h100", num_gpus=1):
+    assert gpu in GPU_TO_FLOPS
+    per_day = mfu * GPU_TO_FLOPS[gpu] * 3600 * 24 * num_gpus
+    return flops / per_day
+
+
+def get_num_parameters(model):
+    return sum(p.numel() for p in model.parameters())
+
+
+def compute_mfu(flops_per_second, gpu="h100"):
+    assert gpu in GPU_TO_FLOPS
+    return flops_per_second / GPU_TO_FLOPS[gpu]

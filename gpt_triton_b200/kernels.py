@@ -1,0 +1,263 @@
+"""The five operators of the reference's ``kernels.py``, backed by libb200gpt (sm_100a).
+
+Same names, positional arguments, assertions and result shapes/dtypes as the reference
+(kernels.py:76, 149, 261, 348, 478), so code written against it keeps working:
+
+    fused_embeddings, fused_layer_norm, fused_ffn, matmul_and_split_qkv, flash_attention_v1
+
+Differences, all deliberate:
+* forward/eval only: a non-zero ``dropout_prob`` raises ``NotImplementedError`` (the
+  reference's modules always pass 0 in eval mode, gpt.py:44, 92, 165);
+* ``matmul_and_split_qkv`` returns q, k, v as strided views into one fused buffer instead of
+  three transposed copies (kernels.py:359-365), and ``flash_attention_v1`` accepts such views;
+* keyword-only extras (``weight_is_nk``, ``merged_heads``, ``out`` ...) used by the model to
+  avoid copies; defaults reproduce the reference's behaviour.
+
+Every operator launches on torch's current CUDA stream and never synchronises.  There is
+no CPU path: tensors must live on a CUDA device and the shared library must be built.
+"""
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, require_cuda, stream_ptr
+
+_lib.load()  # fail at import time, loudly, if the extension is not built
+
+LN_EPS = 1e-5  # kernels.py:106
+
+
+def _no_dropout(p):
+    if p != 0.0:
+        raise NotImplementedError("libb200gpt implements the forward/eval path only: dropout_prob must be 0")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _same_device(*tensors):
+    """Operands must live on one CUDA device; make it current so the launch lands there."""
+    ts = [t for t in tensors if t is not None]
+    dev = ts[0].device
+    for t in ts:
+        assert t.device == dev, f"operands on different devices: {t.device} vs {dev}"
+    return dev
+
+
+# ----------------------------------------------------------------------------- embeddings
+@torch.no_grad()
+def fused_embeddings(x, wte, wpe, dropout_prob=0.0):
+    """z[b, l, :] = wte[x[b, l], :] + wpe[l, :]  (reference kernels.py:76-101)."""
+    _no_dropout(dropout_prob)
+    require_cuda(x, wte, wpe)
+    assert wte.shape[1] == wpe.shape[1]
+    assert x.is_contiguous()
+    assert wte.is_contiguous()
+    assert wpe.is_contiguous()
+    assert wte.dtype == wpe.dtype
+    B, L = x.shape
+    V, H = wte.shape
+    P = wpe.shape[0]
+    assert L <= P, f"sequence length {L} exceeds the position table ({P} rows)"
+    dev = _same_device(x, wte, wpe)
+    if x.dtype != torch.int64:
+        x = x.to(torch.int64)
+    z = torch.empty((B * L, H), device=dev, dtype=wte.dtype)
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_embedding(x.data_ptr(), wte.data_ptr(), wpe.data_ptr(), z.data_ptr(), B, L, V, P, H,
+                                        dtype_code(wte.dtype), None, stream_ptr(dev))
+    check(st, "fused_embeddings")
+    return z.view((B, L, H))
+
+
+# ----------------------------------------------------------------------------- layer norm
+@torch.no_grad()
+def fused_layer_norm(x, weight, bias, *, out_dtype=None):
+    """Row LayerNorm, fp32 statistics, eps 1e-5 (reference kernels.py:149-164)."""
+    require_cuda(x, weight, bias)
+    assert x.is_contiguous()
+    assert weight.is_contiguous()
+    assert bias.is_contiguous()
+    assert weight.shape == bias.shape
+    assert x.shape[-1] == weight.shape[0]
+    assert x.dtype == weight.dtype == bias.dtype
+    out_shape = x.shape
+    H = x.shape[-1]
+    M = x.numel() // H if H else 0
+    dev = _same_device(x, weight, bias)
+    z = torch.empty(x.shape, device=dev, dtype=out_dtype or x.dtype)
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_layernorm(x.data_ptr(), weight.data_ptr(), bias.data_ptr(), z.data_ptr(), M, H, LN_EPS,
+                                        dtype_code(x.dtype), dtype_code(z.dtype), stream_ptr(dev))
+    check(st, "fused_layer_norm")
+    return z.view(out_shape)
+
+
+# ----------------------------------------------------------------------------- GEMM
+class PackedWeight:
+    """A GEMM weight laid out once for the tensor cores: [N, K_padded], 16-bit, K-major.
+
+    ``fused_ffn`` accepts it in place of the [K, N] tensor; the model caches one per
+    parameter so the per-call repacking of ``fused_ffn`` disappears from the hot path.
+    """
+
+    __slots__ = ("data", "K", "N", "storage_dtype")
+
+    def __init__(self, data, K, N, storage_dtype):
+        self.data, self.K, self.N, self.storage_dtype = data, K, N, storage_dtype
+
+
+@torch.no_grad()
+def pack_weight(weight, *, weight_is_nk=False):
+    """Round a [K, N] (or, with weight_is_nk, [N, K]) weight to its 16-bit operand type and
+    store it [N, K_padded] K-major.  fp32 and fp16 weights become fp16 (the rounding the
+    reference applies to every dot operand, kernels.py:234), bf16 stays bf16."""
+    require_cuda(weight)
+    assert weight.dim() == 2 and weight.is_contiguous()
+    K, N = (weight.shape[1], weight.shape[0]) if weight_is_nk else weight.shape
+    kp = (K + 7) // 8 * 8
+    op_dtype = torch.bfloat16 if weight.dtype == torch.bfloat16 else torch.float16
+    if weight_is_nk and weight.dtype == op_dtype and kp == K and weight.data_ptr() % 16 == 0:
+        return PackedWeight(weight, K, N, weight.dtype)  # already in operand layout
+    dev = weight.device
+    packed = torch.empty((N, kp), device=dev, dtype=op_dtype)
+    rows, cols = weight.shape
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_pack_operand(weight.data_ptr(), packed.data_ptr(), rows, cols, cols, kp,
+                                           0 if weight_is_nk else 1, dtype_code(weight.dtype), dtype_code(op_dtype),
+                                           stream_ptr(dev))
+    check(st, "pack_weight")
+    return PackedWeight(packed, K, N, weight.dtype)
+
+
+@torch.no_grad()
+def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=0.0, *, weight_is_nk=False, out=None):
+    """z = [gelu_new](x @ weight + bias) + residual  (reference kernels.py:261-315).
+
+    x (*, K); weight (K, N) -- or (N, K) with ``weight_is_nk=True``, or a PackedWeight;
+    bias (N,); residual viewable as (M, N).  Returns (*, N) in x.dtype.  ``out`` may be a
+    preallocated (M, N) tensor whose rows are strided (last dim contiguous).
+    """
+    _no_dropout(dropout_prob)
+    packed = weight if isinstance(weight, PackedWeight) else None
+    require_cuda(x, None if packed else weight, bias, residual)
+    out_shape_0 = x.shape[:-1]
+    x = x.view((-1, x.shape[-1]))
+    M, K = x.shape
+    if packed is not None:
+        N = packed.N
+        assert K == packed.K
+        assert packed.storage_dtype == x.dtype
+    else:
+        assert weight.is_contiguous()
+        N = weight.shape[0] if weight_is_nk else weight.shape[1]
+        assert x.shape[1] == (weight.shape[1] if weight_is_nk else weight.shape[0])
+        assert weight.dtype == x.dtype
+    assert x.is_contiguous()
+    dev = _same_device(x, packed.data if packed else weight, bias, residual)
+    if out is None:
+        z = torch.empty((M, N), device=dev, dtype=x.dtype)
+    else:
+        z = out
+        assert z.shape == (M, N) and z.dtype == x.dtype and z.stride(1) == 1 and z.device == dev
+    if bias is not None:
+        assert bias.is_contiguous()
+        assert N == bias.shape[0]
+        assert bias.dtype == x.dtype
+    if residual is not None:
+        residual = residual.view((M, N))
+        assert residual.is_contiguous()
+        assert residual.dtype == x.dtype
+    ld_out = z.stride(0) if M > 1 else max(N, z.stride(0))
+    lib = _lib.load()
+    dt = dtype_code(x.dtype)
+    with torch.cuda.device(dev):
+        stream = stream_ptr(dev)
+        if packed is not None and dt != _lib.F32 and K % 8 == 0 and x.data_ptr() % 16 == 0:
+            # operands usable in place: straight to the tensor-core kernel
+            st = lib.b200_gemm(x.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, K,
+                               packed.data.stride(0), N, ld_out, dtype_code(packed.data.dtype), dt, int(bool(add_gelu)),
+                               None, stream)
+        elif packed is not None:
+            # fp32 storage or ragged K: x still has to be rounded/padded into scratch
+            kp = packed.data.stride(0)
+            xs = torch.empty((M, kp), device=dev, dtype=packed.data.dtype)
+            st = lib.b200_pack_operand(x.data_ptr(), xs.data_ptr(), M, K, K, kp, 0, dt, dtype_code(xs.dtype), stream)
+            check(st, "fused_ffn(pack x)")
+            st = lib.b200_gemm(xs.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, kp,
+                               kp, N, ld_out, dtype_code(xs.dtype), dt, int(bool(add_gelu)), None, stream)
+        else:
+            need = lib.b200_ffn_workspace_bytes(M, N, K, int(weight_is_nk), dt)
+            # an unaligned x or weight view needs its operand packed too; ask for the worst case then
+            if x.data_ptr() % 16 or weight.data_ptr() % 16:
+                need = lib.b200_ffn_workspace_bytes(M, N, K, 0, _lib.F32)
+            ws = torch.empty((need,), device=dev, dtype=torch.uint8) if need else None
+            st = lib.b200_ffn(x.data_ptr(), weight.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, ld_out,
+                              int(weight_is_nk), int(bool(add_gelu)), dt, _ptr(ws), need, None, stream)
+    check(st, "fused_ffn")
+    if out is not None:
+        return z
+    return z.view((*out_shape_0, N))
+
+
+# ----------------------------------------------------------------------------- qkv split
+@torch.no_grad()
+def matmul_and_split_qkv(x, weight, bias, num_heads):
+    """c_attn projection and head split (reference kernels.py:348-367).
+
+    Returns q, k, v of logical shape (batch, heads, seqlen, head_size) -- as views into the
+    single (batch, seqlen, 3*hidden) projection output rather than transposed copies.
+    """
+    x = fused_ffn(x, weight, bias=bias)
+    batch_size, seqlen, hidden_size = x.shape
+    assert hidden_size % 3 == 0, hidden_size
+    hidden_size = hidden_size // 3
+    q, k, v = x.split(hidden_size, dim=2)
+    assert hidden_size % num_heads == 0, (hidden_size, num_heads)
+    head_size = hidden_size // num_heads
+    q, k, v = map(lambda t: t.view(batch_size, seqlen, num_heads, head_size).transpose(1, 2), (q, k, v))
+    return q, k, v
+
+
+# ----------------------------------------------------------------------------- attention
+def _bhl_strides(t):
+    """(batch, head, row) element strides of a (B, N, L, H) tensor whose last dim is contiguous."""
+    assert t.stride(3) == 1 or t.shape[3] == 1, "head dimension must be contiguous"
+    return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+@torch.no_grad()
+def flash_attention_v1(q, k, v, dropout_prob=0.0, *, merged_heads=False):
+    """Causal softmax(q k^T / sqrt(H)) v with the reference's 64-key online softmax
+    (reference kernels.py:478-525).  q, k, v: (batch, heads, seqlen, head_size), contiguous or
+    strided views with a contiguous last dim.  Returns a contiguous (B, N, L, H) tensor, or with
+    ``merged_heads=True`` the (B, L, N*H) tensor the reference gets by transposing afterwards
+    (gpt.py:51)."""
+    _no_dropout(dropout_prob)
+    require_cuda(q, k, v)
+    assert q.shape[:2] == k.shape[:2]
+    assert q.shape[-1] == k.shape[-1]
+    assert k.shape == v.shape
+    B, N, Lq, H = q.shape
+    Lk = k.shape[2]
+    assert H in {16, 32, 64, 128, 256}
+    assert Lq == Lk, "the causal mask doubles as the padding mask only when Lq == Lk"
+    assert q.dtype == k.dtype == v.dtype
+    dev = _same_device(q, k, v)
+    if merged_heads:
+        z = torch.empty((B, Lq, N, H), device=dev, dtype=q.dtype)
+        zv = z.transpose(1, 2)
+    else:
+        z = torch.empty((B, N, Lq, H), device=dev, dtype=q.dtype)
+        zv = z
+    scale = 1 / math.sqrt(H)
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), z.data_ptr(), B, N, Lq, H, _bhl_strides(q),
+                                        _bhl_strides(k), _bhl_strides(v), _bhl_strides(zv), scale, dtype_code(q.dtype),
+                                        dtype_code(z.dtype), stream_ptr(dev))
+    check(st, "flash_attention_v1")
+    return z.view(B, Lq, N * H) if merged_heads else z

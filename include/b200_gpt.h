@@ -1,0 +1,119 @@
+/*
+ * C ABI of libb200gpt: the GPT-2 forward hot path as hand-written sm_100a kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given
+ * CUDA stream (a cudaStream_t passed as void*; NULL = the legacy default stream)
+ * and returns immediately with an int status (B200_OK or a B200_ERR_* code); none
+ * of them synchronises, allocates or frees device memory, and none keeps a pointer
+ * after it returns.  All tensors are row-major.  "dtype" arguments are b200_dtype
+ * codes.  Citations name the operator of the reference project (gpt-triton) that an
+ * entry point stands in for, by file:line within that project.
+ */
+#ifndef B200_GPT_H_
+#define B200_GPT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { B200_F32 = 0, B200_F16 = 1, B200_BF16 = 2 } b200_dtype;
+
+enum {
+  B200_OK = 0,
+  B200_ERR_BAD_ARGUMENT = 1, /* a size, dtype code or NULL pointer the op cannot take */
+  B200_ERR_ALIGNMENT = 2,    /* a pointer or leading dimension breaks a stated alignment rule */
+  B200_ERR_CUDA = 3,         /* a CUDA runtime/driver call failed; see b200_last_cuda_error() */
+  B200_ERR_UNSUPPORTED = 4,  /* valid for the reference operator but not built here (e.g. dropout > 0) */
+  B200_ERR_WORKSPACE = 5,    /* workspace NULL or smaller than the *_workspace_bytes() figure */
+  B200_ERR_DEVICE_WAIT = 6   /* a kernel gave up on a bounded on-chip wait; results are invalid */
+};
+
+/* Human-readable name of a status code (static storage). */
+const char* b200_status_string(int status);
+/* cudaGetErrorString of the last failing CUDA call made by this library on this thread. */
+const char* b200_last_cuda_error(void);
+/* ABI version of this header; bumped on any signature change. */
+int b200_abi_version(void);
+
+/*
+ * out[t,:] = wte[ids[t],:] + wpe[t % L,:]   for t in [0, B*L)
+ * Stands in for fused_embeddings (kernels.py:76-101; kernel kernels.py:37-72).
+ * ids: int64 [B*L]; wte [V,H]; wpe [P,H]; out [B*L,H]; all of `dtype`.  Requires L <= P.
+ * An id outside [0,V) writes a zero row and, if bad_id_flag (device int*) is not NULL,
+ * stores 1 there (the reference reads out of bounds instead).
+ */
+int b200_embedding(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t B, int64_t L, int64_t V,
+                   int64_t P, int64_t H, int dtype, int* bad_id_flag, void* stream);
+
+/*
+ * Row LayerNorm with fp32 statistics: out = (x - mean) * rsqrt(var + eps) * w + b.
+ * Stands in for fused_layer_norm (kernels.py:149-164; kernel kernels.py:104-145).
+ * x [M,H], w [H], b [H] of in_dtype; out [M,H] of out_dtype (the reference always has
+ * out_dtype == in_dtype; a 16-bit out_dtype from fp32 input gives the same bits the
+ * following GEMM would have produced by rounding its operand).
+ */
+int b200_layernorm(const void* x, const void* w, const void* b, void* out, int64_t M, int64_t H, float eps,
+                   int in_dtype, int out_dtype, void* stream);
+
+/*
+ * Operand packing for b200_gemm: dst[r, c] = cast(src[r, c]) (transpose == 0) or
+ * dst[c, r] = cast(src[r, c]) (transpose != 0); columns of dst between the logical
+ * width and ld_dst are zero-filled.  src [rows, cols] with leading dimension ld_src.
+ * No counterpart in the reference, whose kernel casts operands on the fly
+ * (kernels.py:229, 234); packing once is how the same rounding is obtained here.
+ * dst_dtype must be 16-bit; f32->f16, f16->f16 and bf16->bf16 are supported.
+ */
+int b200_pack_operand(const void* src, void* dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst,
+                      int transpose, int src_dtype, int dst_dtype, void* stream);
+
+/*
+ * out[M,N] = [gelu_new](A[M,K] . B[N,K]^T + bias[N]) + residual[M,N]
+ * on the tcgen05 tensor cores, fp32 accumulation in tensor memory, epilogue order
+ * bias -> GELU -> residual -> cast.  The compute core behind fused_ffn
+ * (kernels.py:261-315; kernel kernels.py:169-257), with both operands K-major.
+ * A [M,K] (lda) and B [N,K] (ldb) are 16-bit of op_dtype (F16 or BF16); bias,
+ * residual (ld_res) and out (ld_out) are of io_dtype; bias and residual may be NULL.
+ * Alignment: A and B 16-byte aligned, lda and ldb multiples of 8 elements.
+ * status_word: optional device int*, set non-zero if a kernel abandons a bounded wait.
+ */
+int b200_gemm(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+              int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
+              int add_gelu, int* status_word, void* stream);
+
+/*
+ * z = [gelu_new](x @ w + bias) + residual with the reference operator's own layouts:
+ * stands in for fused_ffn (kernels.py:261-315).  x [M,K], w [K,N] (w_is_nk == 0, the
+ * HF Conv1D layout) or [N,K] (w_is_nk != 0, e.g. the tied wte for lm_head,
+ * gpt.py:159-161), bias [N], residual [M,N], out [M,N] with leading dimension ld_out,
+ * all of `dtype`.  Operands are rounded to fp16 (bf16 stays bf16, which gives the same
+ * products) exactly once.  workspace: scratch of at least b200_ffn_workspace_bytes()
+ * bytes, 256-byte aligned, used for packed operands when x or w cannot be fed to the
+ * tensor cores in place (fp32 storage, [K,N] weights, K not a multiple of 8,
+ * unaligned pointers); may be NULL when that figure is 0.
+ */
+size_t b200_ffn_workspace_bytes(int64_t M, int64_t N, int64_t K, int w_is_nk, int dtype);
+int b200_ffn(const void* x, const void* w, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+             int64_t K, int64_t ld_out, int w_is_nk, int add_gelu, int dtype, void* workspace, size_t workspace_bytes,
+             int* status_word, void* stream);
+
+/*
+ * Causal attention with online softmax over 64-key blocks, fp16 operands, fp32
+ * statistics: stands in for flash_attention_v1 (kernels.py:478-525; kernel
+ * kernels.py:375-474).  q, k, v, out are addressed as base + b*s[0] + h*s[1] + l*s[2] + d
+ * with element strides s = {batch, head, row}; the innermost (head_dim) stride is 1.
+ * Contiguous [B,NH,L,D] tensors use {NH*L*D, L*D, D}; views into a fused [B*L, 3*NH*D]
+ * qkv buffer use {L*3*NH*D, D, 3*NH*D}, which is how the split/transposes of
+ * matmul_and_split_qkv (kernels.py:348-367) and the merge of gpt.py:51 cost nothing.
+ * D in {16, 32, 64, 128, 256}; scale is normally 1/sqrt(D).
+ */
+int b200_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L, int64_t D,
+                   const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                   const int64_t o_strides[3], float scale, int in_dtype, int out_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_GPT_H_ */
