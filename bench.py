@@ -1,0 +1,313 @@
+"""Benchmark of the GPT-2 forward hot path: tokens/s of a GPT-2 124M forward (tied lm_head
+included) on synthetic 512 x 300 fp16 batches, per GPU (weak scaling over the GPUs of one node).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]          # this engine (sm_100a kernels)
+    python bench.py --impl reference [...]                       # CPU restatement of the reference
+
+One "step" is one forward pass (embedding -> 12 blocks -> final LayerNorm -> lm_head logits) over
+one batch.  Rank 0 prints one JSON line.  `value` is device-timed with the ids resident in HBM;
+`e2e` is the same pass driven from pinned host ids with the argmax ids read back each step.
+Weights are random-init N(0, 0.02) (output projections scaled by 1/sqrt(24)), ids uniform: no
+dataset or checkpoint is involved.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GPT2_SMALL = dict(vocab_size=50257, block_size=1024, n_layer=12, n_head=12, n_embd=768, dropout=0.1)
+BATCH, SEQ = 512, 300
+CPU_SAMPLE_BATCH = 16  # sequences per CPU-baseline step (the full batch would take minutes per step)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def make_state_dict(dtype):
+    from oracle import gpt2_oracle as orc  # seeded weight generator only (shared with the tests)
+
+    cfg = orc.OracleConfig(**GPT2_SMALL)
+    sd = orc.seeded_state_dict(cfg, seed=0, scale_residual_proj=True)
+    return cfg, {k: v.to(dtype) for k, v in sd.items()}
+
+
+def make_ids(batch, seed):
+    return torch.randint(0, GPT2_SMALL["vocab_size"], (batch, SEQ), generator=torch.Generator().manual_seed(seed))
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.thread = [], None, None
+        self.cmd = ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"]
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=lambda: self.rows.extend(self.proc.stdout), daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=5)
+        sm, mx, reasons = [], [], set()
+        for line in self.rows:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s in sm if s > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(busy)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_forward_tokens_per_s(steps, warmup):
+    """The oracle (CPU restatement of the reference's forward + tied lm_head, all host threads)
+    on CPU_SAMPLE_BATCH x 300 tokens of the benchmark batch per step."""
+    from oracle import gpt2_oracle as orc
+
+    cfg, sd = make_state_dict(torch.float16)
+    ids = make_ids(BATCH, 0)[:CPU_SAMPLE_BATCH]
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        logits = orc.lm_head(sd, orc.gpt_forward(sd, cfg, ids))
+        _ = logits.argmax(-1)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    mean = sum(times) / len(times)
+    return ids.numel() / mean, mean, torch.get_num_threads()
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    tps, mean_s, threads = cpu_forward_tokens_per_s(args.steps, args.warmup)
+    sample = f"{CPU_SAMPLE_BATCH} x {SEQ} tokens of the 512 x 300 batch per step, fp16-rounded operands, fp32 accumulate"
+    print(json.dumps({
+        "impl": "reference", "metric": "gpt2_124m_fwd_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_s * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+        "config": {"workload": "GPT-2 124M forward + tied lm_head, 512 x 300 fp16 (CPU arm: bounded sample per step)",
+                   "batch": CPU_SAMPLE_BATCH, "seq_len": SEQ},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args, rank, world, local_rank):
+    import torch.distributed as dist
+
+    from gpt_triton_b200 import _lib
+    from gpt_triton_b200 import kernels as K
+    from gpt_triton_b200.gpt import FusedGPT, GPTConfig, executed_fwd_flops
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    lib = _lib.load()
+    peaks, peak_kind = load_peaks()
+
+    _, sd = make_state_dict(torch.float16)
+    gcfg = GPTConfig(**GPT2_SMALL)
+    model = FusedGPT(gcfg)
+    model.load_state_dict(sd)
+    model = model.half().to(dev).eval()
+    del sd
+
+    ids_host = make_ids(BATCH, rank).pin_memory()  # every rank its own 512 x 300 batch (weak scaling)
+    ids_dev = ids_host.to(dev)
+    tokens_per_step = BATCH * SEQ
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # ---- device-resident throughput ("value")
+    for _ in range(args.warmup):
+        model.logits(ids_dev)
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    barrier()
+    launches0 = lib.b200_launch_count()
+    sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        logits = model.logits(ids_dev)
+    end.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = lib.b200_launch_count() - launches0
+    ms_total = max_over_ranks(start.elapsed_time(end))
+    ms_per_step = ms_total / args.steps
+    value = world * tokens_per_step / (ms_per_step * 1e-3)
+    del logits
+
+    # ---- end to end: pinned host ids in, argmax ids out, every step
+    out_host = torch.empty((BATCH, SEQ), dtype=torch.int64).pin_memory()
+    gathered = None
+
+    def e2e_step():
+        nonlocal gathered
+        x = ids_host.to(dev, non_blocking=True)
+        am = model.logits(x).argmax(dim=-1)
+        if world > 1:
+            parts = [torch.empty_like(am) for _ in range(world)]
+            dist.all_gather(parts, am)  # 8 bytes per token cross NVLink
+            gathered = parts
+        out_host.copy_(am, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    end.record()
+    barrier()
+    e2e_ms = max_over_ranks(start.elapsed_time(end)) / args.steps
+    e2e_value = world * tokens_per_step / (e2e_ms * 1e-3)
+
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA events around every GEMM launch
+    # of further forward passes, on the stream the kernels are launched on.
+    records = []
+    orig_ffn = K.fused_ffn
+
+    def timed_ffn(x, weight, *a, **kw):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        z = orig_ffn(x, weight, *a, **kw)
+        e.record()
+        m = x.numel() // x.shape[-1]
+        records.append((m, weight.N, weight.K, s, e))
+        return z
+
+    K.fused_ffn = timed_ffn
+    probe_steps = min(3, args.steps)
+    try:
+        for _ in range(probe_steps):
+            model.logits(ids_dev)
+        torch.cuda.synchronize()
+    finally:
+        K.fused_ffn = orig_ffn
+    gemm_ms = sum(s.elapsed_time(e) for *_, s, e in records)
+    gemm_flop = sum(2.0 * m * n * k for m, n, k, _, _ in records)
+    achieved_tflops = gemm_flop / (gemm_ms * 1e-3) / 1e12
+    peak_tflops = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    by_shape = {}
+    for m, n, k, s, e in records:
+        d = by_shape.setdefault((m, n, k), [0.0, 0])
+        d[0] += s.elapsed_time(e)
+        d[1] += 1
+    detail = {f"{m}x{n}x{k}": {"launches_per_step": c // probe_steps, "avg_ms": t / c, "tflops": 2.0 * m * n * k / (t / c * 1e-3) / 1e12}
+              for (m, n, k), (t, c) in by_shape.items()}
+
+    flops = executed_fwd_flops(gcfg, BATCH, SEQ)
+    per_gpu_flops_s = flops / (ms_per_step * 1e-3)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        tps, mean_s, threads = cpu_forward_tokens_per_s(steps=2, warmup=1)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"{CPU_SAMPLE_BATCH} x {SEQ} tokens of the batch, 2 timed passes after 1 warm-up ({mean_s:.2f} s each)"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "gpt2_124m_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp16", "data": "synthetic",
+            "config": {"workload": "GPT-2 124M forward + tied lm_head (logits written), 512 x 300 tokens per GPU, fp16 storage, fp32 accumulate",
+                       "batch_per_gpu": BATCH, "seq_len": SEQ, "global_batch": BATCH * world, "parallelism": f"batch-sharded replicas x{world}",
+                       "l2": "no flush: each step streams > 20 GB of activations and logits, far beyond the 126 MB L2",
+                       "flop_per_step_per_gpu": flops},
+            "mfu": {"of_spec_2250": per_gpu_flops_s / 2250e12, f"of_{peak_kind}_sustained": per_gpu_flops_s / (peak_tflops * 1e12)},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ids_host.numel() * 8,
+                    "d2h_bytes_per_step": out_host.numel() * 8,
+                    "collective": "all_gather of argmax ids" if world > 1 else None},
+            "gpu_launches": int(launches),
+            "roofline": {"kernel": "gemm_tn_kernel (tcgen05, all five GEMM shapes of the forward)", "bound": "tensor",
+                         "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved_tflops / peak_tflops,
+                         "peak_source": f"{peak_kind}: cuBLAS bf16 sustained", "traffic": None, "per_shape": detail},
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_gpu_arm(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -22,6 +22,7 @@ SIGNATURES = {
     "b200_status_string": (ctypes.c_char_p, [c_int]),
     "b200_last_cuda_error": (ctypes.c_char_p, []),
     "b200_abi_version": (c_int, []),
+    "b200_launch_count": (ctypes.c_uint64, []),
     "b200_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_void_p, c_void_p]),
     "b200_layernorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_float, c_int, c_int, c_void_p]),
     "b200_pack_operand": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_void_p]),

@@ -35,6 +35,8 @@ const char* b200_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda);
 
 int b200_abi_version(void) { return 1; }
 
+uint64_t b200_launch_count(void) { return b200::launches_so_far(); }
+
 int b200_embedding(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t B, int64_t L, int64_t V,
                    int64_t P, int64_t H, int dtype, int* bad_id_flag, void* stream) {
   if (B < 0 || L < 0 || V < 1 || P < 1 || H < 0 || !valid_dtype(dtype)) return B200_ERR_BAD_ARGUMENT;

@@ -281,6 +281,7 @@ static int launch_typed(const void* q, const void* k, const void* v, void* out, 
   dim3 grid((unsigned)n_qblocks, (unsigned)bh);
   attention_kernel<D, TIn, TOut><<<grid, NUM_WARPS * 32, smem, stream>>>((const TIn*)q, (const TIn*)k, (const TIn*)v, (TOut*)out, (int)NH,
                                                                         (int)L, sq, sk, sv, so, scale, vec_in, vec_out);
+  note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }
 

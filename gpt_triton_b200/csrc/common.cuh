@@ -124,6 +124,8 @@ __device__ __forceinline__ float gelu_new(float x) {
 inline int status_from_cuda(cudaError_t e) { return e == cudaSuccess ? B200_OK : B200_ERR_CUDA; }
 
 int sm_count();  // cached multiprocessor count of the current device
+void note_launches(int n);  // adds to the library-wide count of kernels launched
+uint64_t launches_so_far();
 
 // ------------------------------------------------------------------ internal launchers
 int launch_embedding(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t T, int64_t L, int64_t V,

@@ -1,9 +1,15 @@
 // HBM-bound kernels of the forward path: embedding gather, LayerNorm, operand packing.
 // All three move each byte once: 128-bit loads/stores, one warp per row, statistics by
 // warp shuffles, grid sized in multiples of the SM count.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b200 {
+
+static std::atomic<uint64_t> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+uint64_t launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
 
 static int g_sm_count = 0;
 int sm_count() {
@@ -62,6 +68,7 @@ static int embedding_typed(const int64_t* ids, const void* wte, const void* wpe,
     embedding_kernel<T, true><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, stream>>>(ids, (const T*)wte, (const T*)wpe, (T*)out, T_rows, L, V, H, flag);
   else
     embedding_kernel<T, false><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, stream>>>(ids, (const T*)wte, (const T*)wpe, (T*)out, T_rows, L, V, H, flag);
+  note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }
 
@@ -175,12 +182,14 @@ static int layernorm_typed(const void* x, const void* w, const void* b, void* ou
 #define B200_LN_CASE(NV)                                                                            \
   if (nv <= NV) {                                                                                   \
     layernorm_vec_kernel<TI, TO, NV><<<g, t, 0, stream>>>(xp, wp, bp, op, M, (int)H, eps);          \
+    note_launches(1);                                                                               \
     return status_from_cuda(cudaGetLastError());                                                    \
   }
     B200_LN_CASE(1) B200_LN_CASE(2) B200_LN_CASE(3) B200_LN_CASE(4) B200_LN_CASE(7) B200_LN_CASE(8) B200_LN_CASE(16)
 #undef B200_LN_CASE
   }
   layernorm_generic_kernel<TI, TO><<<g, t, 0, stream>>>(xp, wp, bp, op, M, H, eps);
+  note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }
 
@@ -249,6 +258,7 @@ static int pack_typed(const void* src, void* dst, int64_t rows, int64_t cols, in
     pack_kernel<TS, TD, true><<<grid, 256, 0, stream>>>((const TS*)src, (TD*)dst, rows, cols, ld_src, ld_dst);
   else
     pack_kernel<TS, TD, false><<<grid, 256, 0, stream>>>((const TS*)src, (TD*)dst, rows, cols, ld_src, ld_dst);
+  note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }
 

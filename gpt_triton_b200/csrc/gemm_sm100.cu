@@ -416,6 +416,7 @@ static int launch_typed(const CUtensorMap& ma, const CUtensorMap& mb, const void
   if (grid > tiles) grid = tiles;
   gemm_tn_kernel<OutT, GELU><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, epi, M, N, K, make_idesc(op_dtype == B200_BF16 ? 1 : 0),
                                                                                  status_word);
+  note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }
 

@@ -37,6 +37,8 @@ const char* b200_status_string(int status);
 const char* b200_last_cuda_error(void);
 /* ABI version of this header; bumped on any signature change. */
 int b200_abi_version(void);
+/* Number of kernels this library has launched in this process so far (all entry points). */
+uint64_t b200_launch_count(void);
 
 /*
  * out[t,:] = wte[ids[t],:] + wpe[t % L,:]   for t in [0, B*L)

@@ -1,0 +1,124 @@
+"""CPU tests: the C-ABI library builds, loads and exports every symbol the header declares (no
+compute without a GPU); the module surface mirrors the reference's; accounting known answers."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT, TINY, load_golden
+
+HEADER = os.path.join(ROOT, "include", "b200_gpt.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    from gpt_triton_b200 import _lib
+    from gpt_triton_b200.build import build
+
+    path = build()
+    assert os.path.exists(path)
+    lib = ctypes.CDLL(path)
+    names = declared_functions()
+    assert len(names) >= 10
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/b200_gpt.h but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes signature table and header disagree"
+    bound = _lib.load()
+    assert bound.b200_abi_version() == 1
+    assert bound.b200_status_string(0) == b"ok"
+    assert bound.b200_status_string(6) == b"a kernel abandoned a bounded wait"
+
+
+def test_argument_checks_need_no_gpu():
+    """Entry points validate sizes/dtypes before touching the device."""
+    from gpt_triton_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.b200_ffn_workspace_bytes(128, 256, 64, 0, _lib.F16) == 256 * 64 * 2  # [K,N] weight needs repacking
+    assert lib.b200_ffn_workspace_bytes(128, 256, 64, 1, _lib.F16) == 0  # both operands usable in place
+    assert lib.b200_ffn_workspace_bytes(128, 256, 64, 1, _lib.F32) == (128 + 256) * 64 * 2
+    assert lib.b200_ffn_workspace_bytes(61, 31, 23, 0, _lib.F32) == (61 * 24 * 2 + 255) // 256 * 256 + (31 * 24 * 2 + 255) // 256 * 256
+    assert lib.b200_layernorm(None, None, None, None, 4, 8, 1e-5, 7, 0, None) == 1  # bad dtype
+    assert lib.b200_layernorm(None, None, None, None, 0, 8, 1e-5, 0, 0, None) == 0  # empty input is a no-op
+    assert lib.b200_embedding(None, None, None, None, 2, 9, 10, 8, 4, 0, None, None) == 1  # L > P
+    strides = (ctypes.c_int64 * 3)(1, 1, 1)
+    assert lib.b200_attention(None, None, None, None, 1, 1, 4, 24, strides, strides, strides, strides, 1.0, 0, 0, None) == 1
+    assert lib.b200_gemm(None, None, None, None, None, 4, 4, 0, 8, 8, 4, 4, 1, 1, 0, None, None) == 1  # K = 0
+    assert lib.b200_ffn(None, None, None, None, None, 0, 4, 4, 4, 0, 0, 1, None, 0, None, None) == 0  # M = 0
+
+
+def test_operators_refuse_cpu_tensors():
+    from gpt_triton_b200 import kernels as K
+
+    with pytest.raises(RuntimeError, match="CUDA"):
+        K.fused_layer_norm(torch.rand(2, 8), torch.ones(8), torch.zeros(8))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        K.fused_embeddings(torch.zeros((1, 2), dtype=torch.long), torch.rand(4, 8), torch.rand(4, 8))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        K.flash_attention_v1(*(torch.rand(1, 1, 4, 16) for _ in range(3)))
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from gpt_triton_b200 import _lib
+
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libb200gpt.so"))
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        _lib.load()
+
+
+def test_module_surface_and_state_dict_layout():
+    from gpt_triton_b200.gpt import FusedGPT, GPTConfig, get_num_parameters
+
+    g = load_golden("accounting")
+    assert GPTConfig() == GPTConfig(vocab_size=50304, block_size=512, n_layer=12, n_head=12, n_embd=768, dropout=0.1)
+    model = FusedGPT(GPTConfig()).eval()
+    assert list(model.state_dict().keys()) == [str(s) for s in g["state_dict_keys"]]
+    assert get_num_parameters(model) == int(g["num_parameters"][0])
+    assert model.get_fwd_flops(1024) == int(g["fwd_flops_1024"][0])
+    r = (model.get_fwd_flops(1024) * 3) / (6 * get_num_parameters(model) * 1024)
+    assert r >= 0.9995  # the reference's test_flops (test.py:136-144)
+    blk = model.blocks[0]
+    assert blk[0].c_attn_weight.shape == (768, 2304) and blk[1].ffn2_weight.shape == (3072, 768)
+
+
+def test_accounting_known_answers():
+    from gpt_triton_b200.gpt import GPU_TO_FLOPS, GPTConfig, compute_mfu, estimate_days, executed_fwd_flops
+
+    g = load_golden("accounting")
+    t = estimate_days(6 * (405 * 10**9) * (15 * 10**12), mfu=0.45, gpu="h100", num_gpus=16_000)
+    assert t == 59.24544994944388 == float(g["estimate_days"][0])  # the reference's test_estimate_days (test.py:147-152)
+    assert compute_mfu(1e14, "a100") == float(g["mfu"][0])
+    assert GPU_TO_FLOPS["b200"] == 2250 * 10**12
+    with pytest.raises(AssertionError):
+        compute_mfu(1.0, "tpu")
+    cfg = GPTConfig(vocab_size=50257, block_size=1024)
+    assert abs(executed_fwd_flops(cfg, 512, 300) / 3.8801e13 - 1) < 1e-3
+    assert abs(executed_fwd_flops(cfg, 512, 300, with_lm_head=False) / 2.6944e13 - 1) < 1e-3
+
+
+def test_huggingface_state_dict_conversion():
+    """A GPT2Model built from a config (no download) converts key for key and loads."""
+    from transformers import GPT2Config, GPT2Model
+
+    from gpt_triton_b200.gpt import FusedGPT, convert_huggingface_to_triton
+
+    hf_cfg = GPT2Config(vocab_size=1024, n_positions=128, n_embd=128, n_layer=2, n_head=4)
+    hf = GPT2Model(hf_cfg)
+    sd, cfg = convert_huggingface_to_triton(hf.state_dict(), hf_cfg)
+    assert (cfg.vocab_size, cfg.block_size, cfg.n_layer, cfg.n_head, cfg.n_embd) == (1024, 128, 2, 4, 128)
+    model = FusedGPT(cfg)
+    missing, unexpected = model.load_state_dict(sd)
+    assert not missing and not unexpected
+    assert torch.equal(model.blocks[1][1].ffn1_weight, hf.h[1].mlp.c_fc.weight)
+    assert torch.equal(model.blocks[0][0].c_attn_bias, hf.h[0].attn.c_attn.bias)
+    hf_cfg.n_ctx = 64
+    assert convert_huggingface_to_triton(hf.state_dict(), hf_cfg)[1].block_size == 64

@@ -1,0 +1,125 @@
+"""GPU parity tests of the whole forward (FusedGPT of gpt_triton_b200.gpt): against the golden
+vectors of the unmodified reference (tiny GPT-2, fp32 and fp16), against the CPU oracle on
+GPT-2-small shapes, and through batch-independence at the benchmark's full size."""
+
+import pytest
+import torch
+
+from conftest import TINY, load_golden
+from oracle import gpt2_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def build_model(cfg_kwargs, dtype, seed=0, random_affine=False, scale_residual_proj=False):
+    from gpt_triton_b200.gpt import FusedGPT, GPTConfig
+
+    ocfg = orc.OracleConfig(**cfg_kwargs)
+    sd = orc.seeded_state_dict(ocfg, seed=seed, random_affine=random_affine, scale_residual_proj=scale_residual_proj)
+    model = FusedGPT(GPTConfig(**cfg_kwargs))
+    model.load_state_dict(sd)
+    model = model.to(dtype).to(DEV).eval()
+    return model, ocfg, {k: v.to(dtype) for k, v in sd.items()}
+
+
+@pytest.mark.parametrize("name,affine", [("tiny_f32", False), ("tiny_f32_affine", True)])
+def test_tiny_fp32_teacher_forced_vs_reference(name, affine):
+    """Every sub-block, fed the reference's own intermediate, matches the reference to 1e-4."""
+    g = load_golden(name)
+    model, cfg, _ = build_model(TINY, torch.float32, random_affine=affine)
+    from gpt_triton_b200 import kernels as K
+
+    ids = g["ids"].to(DEV)
+    emb = K.fused_embeddings(ids, model.wte_weight.data, model.wpe_weight.data)
+    assert torch.equal(emb.cpu(), g["emb"])
+    x = g["emb"]
+    for i in range(cfg.n_layer):
+        a = model.blocks[i][0](x.to(DEV)).cpu()
+        assert (a - g[f"attn{i}"]).abs().max().item() < 1e-4
+        m = model.blocks[i][1](g[f"attn{i}"].to(DEV)).cpu()
+        assert (m - g[f"mlp{i}"]).abs().max().item() < 1e-4
+        x = g[f"mlp{i}"]
+    hid = K.fused_layer_norm(x.to(DEV), model.layer_norm_weight.data, model.layer_norm_bias.data).cpu()
+    assert (hid - g["hidden"]).abs().max().item() < 1e-4
+    logits = model.lm_head(g["hidden"].to(DEV)).cpu()
+    assert (logits - g["logits"]).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("name,affine", [("tiny_f32", False), ("tiny_f32_affine", True)])
+def test_tiny_fp32_end_to_end_vs_reference(name, affine):
+    """Free-running forward + lm_head: argmax bit-exact with the reference; logits within 2e-3
+    (one-ulp fp32 differences flip fp16 operand roundings and the final LayerNorm amplifies
+    them, so the per-op 1e-4 bound does not compose; the CPU oracle shows the same gap)."""
+    g = load_golden(name)
+    model, _, _ = build_model(TINY, torch.float32, random_affine=affine)
+    ids = g["ids"].to(DEV)
+    hidden = model(ids)
+    assert hidden.shape == g["hidden"].shape and hidden.dtype == torch.float32
+    logits = model.lm_head(hidden).cpu()
+    assert (hidden.cpu() - g["hidden"]).abs().max().item() < 5e-3
+    assert (logits - g["logits"]).abs().max().item() < 2e-3
+    assert torch.equal(logits.argmax(-1), g["logits"].argmax(-1))
+    assert torch.equal(model.logits(ids).cpu(), logits)  # deterministic
+
+
+def _argmax_agrees_where_clear(logits, ref, margin):
+    top2 = ref.float().topk(2, dim=-1).values
+    clear = (top2[..., 0] - top2[..., 1]) > margin
+    assert clear.float().mean().item() > 0.5
+    assert torch.equal(logits.float().argmax(-1)[clear], ref.float().argmax(-1)[clear])
+
+
+def test_tiny_fp16_end_to_end_vs_reference():
+    g = load_golden("tiny_f16_affine")
+    model, _, _ = build_model(TINY, torch.float16, random_affine=True)
+    logits = model.logits(g["ids"].to(DEV)).cpu()
+    assert logits.dtype == torch.float16
+    assert (logits.float() - g["logits"].float()).abs().max().item() < 2e-2
+    _argmax_agrees_where_clear(logits, g["logits"], 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tiny_16bit_vs_oracle(dtype):
+    model, cfg, sd = build_model(TINY, dtype, random_affine=True)
+    ids = torch.randint(0, 1024, (3, 100), generator=torch.Generator().manual_seed(1))
+    logits = model.logits(ids.to(DEV)).cpu()
+    ref = orc.lm_head(sd, orc.gpt_forward(sd, cfg, ids))
+    tol = 2e-2 if dtype == torch.float16 else 6.3e-2  # bf16: two ulps at |logit| in [2, 4)
+    assert (logits.float() - ref.float()).abs().max().item() < tol
+    _argmax_agrees_where_clear(logits, ref, tol)
+
+
+GPT2_SMALL = dict(vocab_size=50257, block_size=1024, n_layer=12, n_head=12, n_embd=768, dropout=0.1)
+
+
+def test_gpt2_small_fp16_vs_oracle_and_batch_independence():
+    """GPT-2 124M shapes, fp16, the benchmark's weights (N(0, 0.02), output projections scaled by
+    1/sqrt(24)) and ids (uniform, seed 0).
+    (1) 4 x 300 tokens against the CPU oracle: logits within 2e-2, argmax equal wherever the
+        oracle's top-2 margin exceeds the tolerance.
+    (2) the full 512 x 300 batch: the first and last sequences give bit-identical hidden states
+        to the same sequences run as a small batch (rows are independent, so sharding the batch
+        across GPUs cannot change results)."""
+    model, cfg, sd = build_model(GPT2_SMALL, torch.float16, scale_residual_proj=True)
+    ids = torch.randint(0, 50257, (512, 300), generator=torch.Generator().manual_seed(0))
+    sel = torch.tensor([0, 1, 510, 511])
+    small_hidden = model(ids[sel].to(DEV))
+    small_logits = model.lm_head(small_hidden).cpu()
+    ref_hidden = orc.gpt_forward(sd, cfg, ids[sel])
+    ref_logits = orc.lm_head(sd, ref_hidden)
+    assert (small_hidden.cpu().float() - ref_hidden.float()).abs().max().item() < 2e-2
+    assert (small_logits.float() - ref_logits.float()).abs().max().item() < 2e-2
+    _argmax_agrees_where_clear(small_logits, ref_logits, 2e-2)
+    full_hidden = model(ids.to(DEV))
+    assert torch.equal(full_hidden[sel.to(DEV)], small_hidden)
+    full_logits = model.lm_head(full_hidden)
+    assert full_logits.shape == (512, 300, 50257)
+    assert torch.equal(full_logits[sel.to(DEV)].cpu(), small_logits)
+
+
+def test_training_mode_rejected():
+    model, _, _ = build_model(TINY, torch.float32)
+    model.train()
+    with pytest.raises(NotImplementedError):
+        model(torch.zeros((1, 4), dtype=torch.long, device=DEV))
