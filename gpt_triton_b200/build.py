@@ -13,8 +13,9 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libb200gpt.so")
-SOURCES = ["api.cu", "elementwise.cu", "gemm_sm100.cu", "attention.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(os.path.dirname(PKG_DIR), "include", "b200_gpt.h")]
+SOURCES = ["api.cu", "elementwise.cu", "gemm_sm100.cu", "attention.cu", "attention_sm100.cu"]
+HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "sm100_primitives.cuh"),
+           os.path.join(os.path.dirname(PKG_DIR), "include", "b200_gpt.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",

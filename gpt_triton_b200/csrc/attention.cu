@@ -1,4 +1,6 @@
-// Causal attention with online softmax over 64-key blocks (fp16 operands, fp32 statistics).
+// Causal attention with online softmax over 64-key blocks (fp16 operands, fp32 statistics): the
+// generic kernel (any storage type, head size 16..256, any alignment) on mma.sync tensor-core
+// instructions.  fp16 tensors with head size 64 are routed to the tcgen05/TMA kernel instead.
 //
 // One CTA = 64 query rows of one (batch, head); 4 warps x 16 rows.  Q, K, V are read through
 // (batch, head, row) element strides, so the fused [tokens, 3*hidden] output of the c_attn
@@ -35,6 +37,16 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// exp for the softmax: correctly-rounded-ish expf when the storage type is fp32 (the 1e-4 parity
+// path: a fast exp flips too many fp16 roundings of P), the ex2-based intrinsic otherwise.
+template <typename TIn>
+__device__ __forceinline__ float softmax_exp(float x) {
+  if constexpr (sizeof(TIn) == 4) {
+    return expf(x);
+  } else {
+    return __expf(x);
+  }
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
@@ -159,7 +171,7 @@ attention_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn
       bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 1));
       bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 2));
       const float m_new = fmaxf(m_run[r], bm[r]);
-      mult[r] = __expf(m_run[r] - m_new);
+      mult[r] = softmax_exp<TIn>(m_run[r] - m_new);
       m_run[r] = m_new;
     }
     float psum[2] = {0.f, 0.f};
@@ -168,7 +180,7 @@ attention_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
-        const float p = __expf(s[nt][e] - m_run[r]);
+        const float p = softmax_exp<TIn>(s[nt][e] - m_run[r]);
         s[nt][e] = p;
         psum[r] += p;
       }
@@ -306,6 +318,11 @@ int launch_attention(const void* q, const void* k, const void* v, void* out, int
   using namespace attn;
   if (B == 0 || NH == 0 || L == 0) return B200_OK;
   if (L > 0x7fffffffLL - BLOCK) return B200_ERR_BAD_ARGUMENT;
+  {
+    // tensor-core path for the shapes it covers; everything else takes the generic kernel below
+    const int st = launch_attention_sm100(q, k, v, out, B, NH, L, D, qs, ks, vs, os, scale, in_dtype, out_dtype, nullptr, stream);
+    if (st != B200_ERR_UNSUPPORTED) return st;
+  }
   Strides sq{qs[0], qs[1], qs[2]}, sk{ks[0], ks[1], ks[2]}, sv{vs[0], vs[1], vs[2]}, so{os[0], os[1], os[2]};
   if (in_dtype == B200_F32 && out_dtype == B200_F32) return dispatch_d<float, float>(D, q, k, v, out, B, NH, L, sq, sk, sv, so, scale, stream);
   if (in_dtype == B200_F32 && out_dtype == B200_F16) return dispatch_d<float, __half>(D, q, k, v, out, B, NH, L, sq, sk, sv, so, scale, stream);

@@ -1,0 +1,479 @@
+// Causal flash attention on the 5th-generation tensor cores, head size 64, 16-bit storage.
+//
+// Work item = 128 query rows of one (batch, head).  Persistent CTAs (two per SM) walk the items,
+// longest first.  Per CTA:
+//   warp 0      TMA producer: the 128x64 Q tile (double-buffered) and, per 64-key block, the K and
+//               V tiles (3-stage ring), all 128-byte swizzled, straight out of the strided q/k/v
+//               views (4-D tensor maps: head_dim, row, head, batch); no multicast
+//   warp 1      tcgen05.mma issuer: S = Q K^T (128x64, fp32, tensor memory, double-buffered, issued
+//               one block ahead) and PV = P V (128x64, fresh accumulator per block, double-buffered)
+//   warps 2-5   softmax: one thread per query row.  Reads S from tensor memory, keeps the running
+//               maximum/denominator in fp32, writes P = exp(s - max) rounded to fp16 into shared
+//               memory in the swizzled K-major operand layout, and folds the previous block's PV
+//               into its fp32 output row: o = o * exp(m_old - m_new) + PV.
+// The softmax runs over 64-key blocks with P rounded relative to the running maximum of each
+// block, which is the arithmetic of the reference's flash_attention_v1 kernel (kernels.py:417-474
+// of the reference); blocks above the diagonal are skipped.  Every mbarrier wait is bounded.
+#include "sm100_primitives.cuh"
+
+namespace b200 {
+namespace attn100 {
+
+using namespace sm100;
+
+constexpr int D = 64;
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 64;
+constexpr int KV_STAGES = 3;
+constexpr int Q_BYTES = BLOCK_M * D * 2;        // 16 KB
+constexpr int KV_TILE_BYTES = BLOCK_N * D * 2;  // 8 KB each for K and V
+constexpr int KV_STAGE_BYTES = 2 * KV_TILE_BYTES;
+constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;  // 16 KB
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 256;  // S[2] (64 columns each) + PV[2] (64 columns each)
+constexpr int CTRL_BYTES = 256;
+constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES + 1024 + CTRL_BYTES;
+
+struct Params {
+  void* out;
+  int64_t so_b, so_h, so_l;
+  int B, NH, L;
+  float scale_log2e;  // softmax scale times log2(e)
+  int out_vec32;      // output rows may be written with 32-byte stores
+  int q_head_inner, k_head_inner, v_head_inner;  // tensor map dimension order is {D, head, row, batch} instead of {D, row, head, batch}
+  int* status_word;
+};
+
+// K-major operand, 128-byte swizzle (rows of 128 bytes, 8-row groups of 1024 bytes).
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// MN-major operand, 128-byte swizzle: 64 contiguous MN elements per 128-byte row, 8 K-rows per 1024-byte
+// group; groups along K are `stride byte offset` apart, 64-wide MN chunks `leading byte offset` apart
+// (one chunk only here).  This is how a [keys, head_dim] V tile serves as the B operand of P V.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(1024 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: fp32 accumulator, M = 128, N = 64.
+__host__ __device__ constexpr uint32_t idesc(int a_fmt, int b_fmt, int b_mn_major) {
+  return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(BLOCK_N >> 3) << 17) |
+         ((uint32_t)(BLOCK_M >> 4) << 24);
+}
+
+struct Item {
+  int b, h, q0, nblk;
+};
+// Items ordered by decreasing row-tile index (the longest causal rows first), then (batch, head).
+__device__ __forceinline__ Item decode_item(int64_t idx, int bh_total, int n_qt, int NH, int L) {
+  const int qt = n_qt - 1 - (int)(idx / bh_total);
+  const int bh = (int)(idx % bh_total);
+  Item it;
+  it.b = bh / NH;
+  it.h = bh % NH;
+  it.q0 = qt * BLOCK_M;
+  const int last_row = min(it.q0 + BLOCK_M, L) - 1;
+  it.nblk = last_row / BLOCK_N + 1;
+  return it;
+}
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack_out(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack_out<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_out<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, Params p, uint32_t idesc_s, uint32_t idesc_pv) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t smem_q = base;                                 // [2][128][64]
+  const uint32_t smem_kv = smem_q + 2 * Q_BYTES;                // [KV_STAGES]{K[64][64], V[64][64]}
+  const uint32_t smem_p = smem_kv + KV_STAGES * KV_STAGE_BYTES;  // [128][64] fp16
+  uint8_t* ctrl = smem + 2 * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES;
+  const uint32_t bars = smem_u32(ctrl);
+  const uint32_t bar_q_full = bars;                  // [2]
+  const uint32_t bar_q_empty = bars + 16;            // [2]
+  const uint32_t bar_kv_full = bars + 32;            // [KV_STAGES]
+  const uint32_t bar_kv_empty = bar_kv_full + 8 * KV_STAGES;
+  const uint32_t bar_s_full = bar_kv_empty + 8 * KV_STAGES;  // [2]
+  const uint32_t bar_s_empty = bar_s_full + 16;      // [2]
+  const uint32_t bar_p_full = bar_s_empty + 16;      // [1]
+  const uint32_t bar_p_empty = bar_p_full + 8;       // [1]
+  const uint32_t bar_pv_full = bar_p_empty + 8;      // [2]
+  const uint32_t bar_pv_empty = bar_pv_full + 16;    // [2]
+  constexpr int BAR_BYTES = 32 + 16 * KV_STAGES + 16 + 16 + 8 + 8 + 16 + 16;
+  static_assert(BAR_BYTES + 16 <= CTRL_BYTES, "control block too small");
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + BAR_BYTES);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + BAR_BYTES + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.L + BLOCK_M - 1) / BLOCK_M;
+  const int bh_total = p.B * p.NH;
+  const int64_t n_items = (int64_t)n_qt * bh_total;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_q_full + 8 * i, 1);
+      mbar_init(bar_q_empty + 8 * i, 1);
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_s_empty + 8 * i, 4);
+      mbar_init(bar_pv_full + 8 * i, 1);
+      mbar_init(bar_pv_empty + 8 * i, 4);
+    }
+    for (int i = 0; i < KV_STAGES; ++i) {
+      mbar_init(bar_kv_full + 8 * i, 1);
+      mbar_init(bar_kv_empty + 8 * i, 1);
+    }
+    mbar_init(bar_p_full, 4);
+    mbar_init(bar_p_empty, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;         // S[buf] at columns buf*64
+  const uint32_t tmem_pv = tmem_base + 128;  // PV[buf] at columns 128 + buf*64
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t qi = 0, ki = 0;
+      bool alive = true;
+      for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
+        const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
+        const uint32_t qb = qi & 1;
+        if (!mbar_wait(bar_q_empty + 8 * qb, ((qi >> 1) & 1) ^ 1u, abort_flag, p.status_word, 11)) break;
+        mbar_arrive_expect_tx(bar_q_full + 8 * qb, Q_BYTES);
+        tma_load_4d(smem_q + qb * Q_BYTES, &map_q, bar_q_full + 8 * qb, 0, p.q_head_inner ? it.h : it.q0, p.q_head_inner ? it.q0 : it.h, it.b);
+        ++qi;
+        for (int j = 0; j < it.nblk; ++j) {
+          const uint32_t st = ki % KV_STAGES;
+          if (!mbar_wait(bar_kv_empty + 8 * st, ((ki / KV_STAGES) & 1) ^ 1u, abort_flag, p.status_word, 12)) {
+            alive = false;
+            break;
+          }
+          mbar_arrive_expect_tx(bar_kv_full + 8 * st, KV_STAGE_BYTES);
+          tma_load_4d(smem_kv + st * KV_STAGE_BYTES, &map_k, bar_kv_full + 8 * st, 0, p.k_head_inner ? it.h : j * BLOCK_N, p.k_head_inner ? j * BLOCK_N : it.h, it.b);
+          tma_load_4d(smem_kv + st * KV_STAGE_BYTES + KV_TILE_BYTES, &map_v, bar_kv_full + 8 * st, 0, p.v_head_inner ? it.h : j * BLOCK_N, p.v_head_inner ? j * BLOCK_N : it.h, it.b);
+          ++ki;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t qi = 0, ks = 0, kp = 0, si = 0, pi = 0;
+      bool alive = true;
+      // S_{next} = Q . K^T into S[si & 1]
+      auto issue_s = [&](uint32_t qb) -> bool {
+        const uint32_t st = ks % KV_STAGES;
+        if (!mbar_wait(bar_kv_full + 8 * st, (ks / KV_STAGES) & 1, abort_flag, p.status_word, 13)) return false;
+        const uint32_t sb = si & 1;
+        if (!mbar_wait(bar_s_empty + 8 * sb, ((si >> 1) & 1) ^ 1u, abort_flag, p.status_word, 14)) return false;
+        tc_fence_after();
+        const uint64_t da = desc_kmajor(smem_q + qb * Q_BYTES);
+        const uint64_t db = desc_kmajor(smem_kv + st * KV_STAGE_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s + sb * BLOCK_N, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc_s, (uint32_t)(k != 0));
+        umma_commit(bar_s_full + 8 * sb);
+        ++si;
+        ++ks;
+        return true;
+      };
+      for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
+        const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
+        const uint32_t qb = qi & 1;
+        if (!mbar_wait(bar_q_full + 8 * qb, (qi >> 1) & 1, abort_flag, p.status_word, 15)) break;
+        if (!issue_s(qb)) break;
+        for (int j = 0; j < it.nblk; ++j) {
+          if (j + 1 < it.nblk) {
+            if (!issue_s(qb)) {
+              alive = false;
+              break;
+            }
+          } else {
+            umma_commit(bar_q_empty + 8 * qb);  // every S of this item is issued: Q is free once they finish
+          }
+          // PV_j = P . V_j into PV[pi & 1]
+          const uint32_t st = kp % KV_STAGES;
+          const uint32_t ob = pi & 1;
+          if (!mbar_wait(bar_p_full, pi & 1, abort_flag, p.status_word, 16) ||
+              !mbar_wait(bar_pv_empty + 8 * ob, ((pi >> 1) & 1) ^ 1u, abort_flag, p.status_word, 17)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t da = desc_kmajor(smem_p);
+          const uint64_t db = desc_mnmajor(smem_kv + st * KV_STAGE_BYTES + KV_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BLOCK_N / 16; ++k) {
+            // A: +16 keys = +32 bytes inside the swizzled row; B: +16 keys = two 8-key groups = +2048 bytes
+            umma_f16(tmem_pv + ob * D, da + (uint64_t)(2 * k), db + (uint64_t)(128 * k), idesc_pv, (uint32_t)(k != 0));
+          }
+          umma_commit(bar_pv_full + 8 * ob);
+          umma_commit(bar_kv_empty + 8 * st);
+          umma_commit(bar_p_empty);
+          ++pi;
+          ++kp;
+        }
+        ++qi;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps: one thread per query row
+    const int quarter = warp & 3;
+    const int r_in_tile = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t p_row = smem_p + (uint32_t)r_in_tile * 128u;
+    const uint32_t sw = (uint32_t)(r_in_tile & 7);
+    uint32_t it_count = 0;  // 64-key blocks processed so far by this CTA
+    bool alive = true;
+    for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
+      const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
+      const int row = it.q0 + r_in_tile;
+      float o[D];
+#pragma unroll
+      for (int i = 0; i < D; ++i) o[i] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f, mult_prev = 0.f;
+      for (int j = 0; j < it.nblk; ++j, ++it_count) {
+        const uint32_t sb = it_count & 1;
+        if (!mbar_wait(bar_s_full + 8 * sb, (it_count >> 1) & 1, abort_flag, p.status_word, 18)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t s_addr = tmem_s + lane_addr + sb * BLOCK_N;
+        const int k0 = j * BLOCK_N;
+        const bool need_mask = k0 + BLOCK_N - 1 > it.q0;  // some key of this block lies above some row's diagonal
+        // pass 1: block maximum of the raw scores (the scale is positive, so it commutes with max)
+        float bm = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(v[i]);
+            if (need_mask && k0 + c * 32 + i > row) x = -INFINITY;
+            bm = fmaxf(bm, x);
+          }
+        }
+        const float m_new = fmaxf(m_run, bm * p.scale_log2e);  // running maximum, in log2 units
+        const float mult = ex2f(m_run - m_new);
+        m_run = m_new;
+        // P buffer must have been consumed by the previous block's P V
+        if (!mbar_wait(bar_p_empty, (it_count & 1) ^ 1u, abort_flag, p.status_word, 19)) {
+          alive = false;
+          break;
+        }
+        // pass 2: p = exp(s - max), row sum in fp32, P rounded to fp16 into the swizzled operand tile
+        float psum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0 = fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new);
+            float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m_new);
+            if (need_mask) {
+              if (k0 + c * 32 + i > row) x0 = -INFINITY;
+              if (k0 + c * 32 + i + 1 > row) x1 = -INFINITY;
+            }
+            const float p0 = ex2f(x0), p1 = ex2f(x1);
+            psum += p0 + p1;
+            __half2 h = __floats2half2_rn(p0, p1);
+            w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t chunk = (uint32_t)(c * 4 + g);
+            st_shared_v4(p_row + ((chunk ^ sw) << 4), w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+          }
+        }
+        // S[sb] is free; P is complete
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar_s_empty + 8 * sb);
+          mbar_arrive(bar_p_full);
+        }
+        l_run = l_run * mult + psum;
+        // fold the previous block's P V:  o = o * mult_prev + PV_{j-1}
+        if (j > 0) {
+          const uint32_t ob = (it_count - 1) & 1;
+          if (!mbar_wait(bar_pv_full + 8 * ob, ((it_count - 1) >> 1) & 1, abort_flag, p.status_word, 20)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_pv + lane_addr + ob * D + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], mult_prev, __uint_as_float(v[i]));
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_pv_empty + 8 * ob);
+        }
+        mult_prev = mult;
+      }
+      if (!alive) break;
+      // last block's P V, then normalise and store the row
+      {
+        const uint32_t ob = (it_count - 1) & 1;
+        if (!mbar_wait(bar_pv_full + 8 * ob, ((it_count - 1) >> 1) & 1, abort_flag, p.status_word, 21)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_pv + lane_addr + ob * D + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], mult_prev, __uint_as_float(v[i]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_pv_empty + 8 * ob);
+      }
+      if (row < p.L) {
+        const float inv = 1.0f / l_run;
+        T* dst = reinterpret_cast<T*>(p.out) + (int64_t)it.b * p.so_b + (int64_t)it.h * p.so_h + (int64_t)row * p.so_l;
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) w[i] = pack_out<T>(o[2 * i] * inv, o[2 * i + 1] * inv);
+        if (p.out_vec32) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) st_global_v8(dst + g * 16, &w[g * 8]);
+        } else {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// 4-D map over a strided (batch, head, row) view with contiguous head_dim.  The two middle dimensions are
+// ordered by ascending stride ({D, row, head, batch} for contiguous [B, NH, L, D] tensors, {D, head, row, batch}
+// for views into a fused [B, L, 3*NH*D] projection); *head_inner tells the kernel which order was used.
+static int make_map(CUtensorMap* map, const void* ptr, int64_t B, int64_t NH, int64_t L, const int64_t* s, int box_rows, int dtype,
+                    int* head_inner) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return B200_ERR_CUDA;
+  *head_inner = s[1] < s[2];
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)NH, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)s[2] * 2, (cuuint64_t)s[1] * 2, (cuuint64_t)s[0] * 2};
+  cuuint32_t box[4] = {(cuuint32_t)D, (cuuint32_t)box_rows, 1, 1};
+  if (*head_inner) {
+    dims[1] = (cuuint64_t)NH, dims[2] = (cuuint64_t)L;
+    strides[0] = (cuuint64_t)s[1] * 2, strides[1] = (cuuint64_t)s[2] * 2;
+    box[1] = 1, box[2] = (cuuint32_t)box_rows;
+  }
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(ptr), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_CUDA;
+}
+
+static bool view_ok(const void* ptr, const int64_t* s, int64_t B, int64_t NH) {
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
+  // TMA wants 16-byte multiples for every stride; a stride of a size-1 dimension is never used but must still encode
+  for (int i = 0; i < 3; ++i)
+    if (s[i] % 8 != 0 || s[i] <= 0 || (uint64_t)s[i] * 2 >= (1ull << 40)) return false;
+  (void)B;
+  (void)NH;
+  return true;
+}
+
+}  // namespace attn100
+
+// Returns B200_ERR_UNSUPPORTED when the problem does not fit this kernel (the caller then takes the generic one).
+int launch_attention_sm100(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L, int64_t Dh,
+                           const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int in_dtype,
+                           int out_dtype, int* status_word, cudaStream_t stream) {
+  using namespace attn100;
+  if (Dh != D || in_dtype != out_dtype || in_dtype != B200_F16) return B200_ERR_UNSUPPORTED;
+  if (!view_ok(q, qs, B, NH) || !view_ok(k, ks, B, NH) || !view_ok(v, vs, B, NH) || !view_ok(out, os, B, NH)) return B200_ERR_UNSUPPORTED;
+  if (B * NH > 0x7fffffffLL || L > 0x7fffff00LL || B > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  Params p;
+  int st = make_map(&mq, q, B, NH, L, qs, BLOCK_M, in_dtype, &p.q_head_inner);
+  if (st == B200_OK) st = make_map(&mk, k, B, NH, L, ks, BLOCK_N, in_dtype, &p.k_head_inner);
+  if (st == B200_OK) st = make_map(&mv, v, B, NH, L, vs, BLOCK_N, in_dtype, &p.v_head_inner);
+  if (st != B200_OK) return B200_ERR_UNSUPPORTED;  // e.g. strides the tensor map cannot express
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attention_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return B200_ERR_CUDA;
+    attr_set = true;
+  }
+  p.out = out;
+  p.so_b = os[0], p.so_h = os[1], p.so_l = os[2];
+  p.B = (int)B, p.NH = (int)NH, p.L = (int)L;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.out_vec32 = (reinterpret_cast<uintptr_t>(out) & 31) == 0 && os[0] % 16 == 0 && os[1] % 16 == 0 && os[2] % 16 == 0;
+  p.status_word = status_word;
+  const int64_t n_items = ((L + BLOCK_M - 1) / BLOCK_M) * B * NH;
+  int64_t grid = (int64_t)sm_count() * 2;
+  if (grid > n_items) grid = n_items;
+  attention_sm100_kernel<__half><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p, idesc(0, 0, 0), idesc(0, 0, 1));
+  note_launches(1);
+  return status_from_cuda(cudaGetLastError());
+}
+
+}  // namespace b200

@@ -5,19 +5,19 @@
 //               completion by mbarrier transaction bytes (no multicast anywhere)
 //   warp 1      allocates the 512 tensor-memory columns and issues tcgen05.mma (one thread);
 //               tcgen05.commit releases smem stages and publishes finished accumulators
-//   warps 2-5   epilogue: tcgen05.ld the 128x256 fp32 accumulator (one row per thread),
-//               bias -> GELU -> residual -> cast -> global store
+//   warps 2-9   epilogue: tcgen05.ld the 128x256 fp32 accumulator (one row per thread, each warp
+//               128 of the 256 columns), bias -> GELU -> residual -> cast -> global store.  The
+//               residual rows are fetched into registers and the bias into shared memory before
+//               the accumulator is awaited, so their latency hides behind the main loop.
 // Two 128x256 accumulators (2 x 256 columns) let the epilogue of tile i overlap the main
 // loop of tile i+1.  Every wait on an mbarrier is bounded; a wait that gives up raises a
 // CTA-wide abort flag, reports through status_word and the kernel drains and exits.
-#include <cuda.h>
-
-#include <mutex>
-
-#include "common.cuh"
+#include "sm100_primitives.cuh"
 
 namespace b200 {
 namespace gemm {
+
+using namespace sm100;
 
 constexpr int BM = 128;
 constexpr int BN = 256;
@@ -27,97 +27,15 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int B_STAGE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int NUM_THREADS = 192;
-constexpr int NUM_EPI_WARPS = 4;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_THREADS = 32 * (2 + NUM_EPI_WARPS);
+constexpr int EPI_COLS = BN / (NUM_EPI_WARPS / 4);  // columns per epilogue warp
+constexpr int EPI_CHUNKS = EPI_COLS / 32;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 16;  // row tiles per raster group (keeps a group's A rows and B columns L2-resident)
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another one timed out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-      *abort_flag = 1;
-      if (status_word) atomicCAS(status_word, 0, where);
-      return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-// D[tmem] (+)= A[smem] . B[smem]^T, 128 x 256 x 16, issued by one thread.
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// mbarrier arrives once all tcgen05.mma issued so far by this thread have completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives row (lane base + i).
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+constexpr int CTRL_BYTES = 256;  // mbarriers, tensor-memory base, abort flag
+constexpr int BIAS_BYTES = 2 * BN * 4;  // bias of the current and the next tile, as fp32
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + CTRL_BYTES + BIAS_BYTES;
 
 // Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 bytes, an
 // 8-row group is 1024 bytes (stride byte offset), leading byte offset unused for swizzled
@@ -162,48 +80,121 @@ struct EpilogueArgs {
   int64_t ld_res, ld_out;
 };
 
-// Epilogue for one thread's 32 consecutive columns of one row.
+// x * sigmoid(2y), y = sqrt(2/pi) (x + 0.044715 x^3): algebraically the reference's
+// 0.5 x (1 + tanh(y)) with tanh(y) = 2 sigmoid(2y) - 1 (kernels.py:15-26 of the reference),
+// evaluated with one ex2 and one reciprocal on the special-function unit.
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float c0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;  // -2 sqrt(2/pi) log2(e)
+  const float c1 = c0 * 0.044715f;
+  const float z = x * fmaf(x * x, c1, c0);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
+}
+
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <typename OutT>
+__device__ __forceinline__ float2 unpack2(uint32_t u);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+  return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+}
+
+// How a thread may store its 32-column pieces of an output row.
+enum StoreMode { STORE_SCALAR = 0, STORE_16B = 1, STORE_32B = 2 };
+
+// Residual of one thread's row for its warp's EPI_COLS columns, fetched ahead of the accumulator.
+// Only used on the wide path with a 16-bit output type: EPI_COLS halves = EPI_COLS/8 uint4.
+struct ResidualRegs {
+  uint4 v[EPI_COLS / 8];
+};
+
+// One thread, one row, 32 consecutive columns starting at col0: acc (+bias) -> GELU -> (+residual) -> store.
+// `bias_s` points at this chunk's 32 fp32 bias values in shared memory (zeros when there is no bias).
 template <typename OutT, bool GELU>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const EpilogueArgs<OutT>& e, int64_t row, int col0,
-                                               int64_t M, int64_t N, bool vec_ok) {
-  if (row >= M || col0 >= N) return;
-  const bool full = col0 + 32 <= N;
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const float* bias_s, const EpilogueArgs<OutT>& e,
+                                               const uint4* res_regs, int64_t row, int col0, int64_t N, int mode) {
+  float f[32];
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 b = *reinterpret_cast<const float4*>(bias_s + j);
+    f[j] = __uint_as_float(acc[j]) + b.x;
+    f[j + 1] = __uint_as_float(acc[j + 1]) + b.y;
+    f[j + 2] = __uint_as_float(acc[j + 2]) + b.z;
+    f[j + 3] = __uint_as_float(acc[j + 3]) + b.w;
+  }
+  if (GELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = gelu_fast(f[j]);
+  }
   OutT* orow = e.out + row * e.ld_out + col0;
-  const OutT* rrow = e.residual ? e.residual + row * e.ld_res + col0 : nullptr;
-  const OutT* brow = e.bias ? e.bias + col0 : nullptr;
-  if (full && vec_ok) {
+  const bool full = col0 + 32 <= N;
+  if (mode != STORE_SCALAR && full) {
+    if constexpr (sizeof(OutT) == 2) {
+      if (res_regs) {
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      float f[8];
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t* rw = reinterpret_cast<const uint32_t*>(&res_regs[g]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(acc[g * 8 + j]);
-      if (brow) {
-        float b[8];
-        load8(brow + g * 8, b);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] += b[j];
+          for (int j = 0; j < 4; ++j) {
+            const float2 r = unpack2<OutT>(rw[j]);
+            f[g * 8 + 2 * j] += r.x;
+            f[g * 8 + 2 * j + 1] += r.y;
+          }
+        }
       }
-      if (GELU) {
+      uint32_t w[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = gelu_new(f[j]);
-      }
-      if (rrow) {
-        float r[8];
-        load8(rrow + g * 8, r);
+      for (int j = 0; j < 16; ++j) w[j] = pack2<OutT>(f[2 * j], f[2 * j + 1]);
+      if (mode == STORE_32B) {
+        st_global_v8(orow, reinterpret_cast<const uint32_t(&)[8]>(w[0]));
+        st_global_v8(orow + 16, reinterpret_cast<const uint32_t(&)[8]>(w[8]));
+      } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] += r[j];
+        for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
       }
-      store8(orow + g * 8, f);
+    } else {
+      if (e.residual) {
+        const float* rrow = reinterpret_cast<const float*>(e.residual) + row * e.ld_res + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 r = *reinterpret_cast<const float4*>(rrow + j);
+          f[j] += r.x, f[j + 1] += r.y, f[j + 2] += r.z, f[j + 3] += r.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
     }
   } else {
+    const OutT* rrow = e.residual ? e.residual + row * e.ld_res + col0 : nullptr;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       if (col0 + j < N) {
-        float f = __uint_as_float(acc[j]);
-        if (brow) f += to_float(brow[j]);
-        if (GELU) f = gelu_new(f);
-        if (rrow) f += to_float(rrow[j]);
-        orow[j] = from_float<OutT>(f);
+        float v = f[j];
+        if (rrow) v += to_float(rrow[j]);
+        orow[j] = from_float<OutT>(v);
       }
     }
   }
@@ -221,13 +212,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t smem_a = base;
   const uint32_t smem_b = base + STAGES * A_STAGE_BYTES;
   uint8_t* ctrl = smem + STAGES * STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);  // full[S], empty[S], acc_full[2], acc_empty[2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);  // full[S], empty[S], acc_full[2], acc_empty[2], bias_ready[2]
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * STAGES;
   const uint32_t bar_acc_full = bar_empty + 8 * STAGES;
   const uint32_t bar_acc_empty = bar_acc_full + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * STAGES + 4));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * (2 * STAGES + 4) + 8);
+  const uint32_t bar_bias = bar_acc_empty + 16;
+  static_assert(8 * (2 * STAGES + 6) + 16 <= CTRL_BYTES, "control block too small");
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * STAGES + 6));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * (2 * STAGES + 6) + 8);
+  float* bias_smem = reinterpret_cast<float*>(ctrl + CTRL_BYTES);  // [2][BN]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -245,6 +239,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_acc_full + 8 * a, 1);
       mbar_init(bar_acc_empty + 8 * a, NUM_EPI_WARPS);
+      mbar_init(bar_bias + 8 * a, NUM_EPI_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -323,29 +318,58 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
-    const int quarter = warp & 3;  // a warp may only touch tensor-memory lanes [32*(warp%4), +32)
+    const int quarter = warp & 3;             // a warp may only touch tensor-memory lanes [32*(warp%4), +32)
+    const int col_half = (warp - 2) >> 2;     // which EPI_COLS-wide column range of the tile this warp owns
+    const int epi_tid = (int)threadIdx.x - 64;  // 0 .. 32*NUM_EPI_WARPS-1
     int acc = 0;
     uint32_t acc_phase = 0;
-    const int esz = (int)sizeof(OutT);
-    const bool vec_ok = aligned16(epi.out) && (epi.ld_out * esz) % 16 == 0 &&
-                        (!epi.residual || (aligned16(epi.residual) && (epi.ld_res * esz) % 16 == 0)) &&
-                        (!epi.bias || aligned16(epi.bias));
+    constexpr int esz = (int)sizeof(OutT);
+    const uintptr_t out_al = reinterpret_cast<uintptr_t>(epi.out) | (uintptr_t)(epi.ld_out * esz);
+    const uintptr_t res_al = epi.residual ? (reinterpret_cast<uintptr_t>(epi.residual) | (uintptr_t)(epi.ld_res * esz)) : 0;
+    int mode = STORE_SCALAR;
+    if (((out_al | res_al) & 15) == 0) mode = (esz == 2 && (out_al & 31) == 0) ? STORE_32B : STORE_16B;
     for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
+      const int64_t row = (int64_t)tc.m * BM + quarter * 32 + lane;
+      const int col_base = tc.n * BN + col_half * EPI_COLS;
+      const bool row_ok = row < M;
+      // Prefetch what does not depend on the accumulator: bias -> shared memory, residual -> registers.
+      float* bias_s = bias_smem + acc * BN;
+      for (int i = epi_tid; i < BN; i += 32 * NUM_EPI_WARPS) {
+        const int c = tc.n * BN + i;
+        bias_s[i] = (epi.bias && c < N) ? to_float(epi.bias[c]) : 0.f;
+      }
+      ResidualRegs res;
+      const bool res_in_regs = esz == 2 && epi.residual && mode != STORE_SCALAR && row_ok;
+      if (res_in_regs) {
+        const OutT* rrow = epi.residual + row * epi.ld_res + col_base;
+#pragma unroll
+        for (int i = 0; i < EPI_COLS / 8; ++i) {
+          if (col_base + (i / 4) * 32 + 32 <= N) res.v[i] = *reinterpret_cast<const uint4*>(rrow + i * 8);
+        }
+      }
+      // bias visible to all epilogue warps (an mbarrier, not bar.sync: its wait is bounded like every other)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_bias + 8 * acc);
+      if (!mbar_wait(bar_bias + 8 * acc, acc_phase, abort_flag, status_word, 5)) break;
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, status_word, 4)) break;
       tc_fence_after();
-      const int64_t row = (int64_t)tc.m * BM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_half * EPI_COLS);
+#pragma unroll
+      for (int c = 0; c < EPI_CHUNKS; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
         tmem_ld_wait();
-        epilogue_chunk<OutT, GELU>(v, epi, row, tc.n * BN + c * 32, M, N, vec_ok);
+        if (c == EPI_CHUNKS - 1) {
+          // accumulator fully read: hand it back to the MMA warp before doing the last chunk's math
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        }
+        const int col0 = col_base + c * 32;
+        if (row_ok && col0 < N)
+          epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, res_in_regs ? &res.v[c * 4] : nullptr, row, col0, N, mode);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
@@ -370,22 +394,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
 // 2-D map over a row-major [rows, cols] 16-bit matrix with leading dimension ld; box = 64 columns x box_rows.
 static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows, int op_dtype) {
   EncodeTiledFn fn = get_encode_fn();

@@ -153,11 +153,12 @@ class FusedGPT(_EvalOnly):
     @torch.no_grad()
     def lm_head(self, hidden):
         """hidden (batch, seqlen, n_embd) -> logits (batch, seqlen, vocab_size) with the tied
-        embedding matrix.  The logits buffer's row pitch is padded to a multiple of 8 elements so
-        every row starts 16-byte aligned; the result is the [..., :vocab_size] view of it."""
+        embedding matrix.  The logits buffer's row pitch is padded to a multiple of 64 elements so
+        every row starts 128-byte aligned (wide stores); the result is the [..., :vocab_size] view
+        of it."""
         B, L, h = hidden.shape
         V = self.config.vocab_size
-        pitch = (V + 7) // 8 * 8
+        pitch = (V + 63) // 64 * 64
         buf = torch.empty((B * L, pitch), device=hidden.device, dtype=hidden.dtype)
         K.fused_ffn(hidden.reshape(B * L, h), self._operand(self.wte_weight, weight_is_nk=True), out=buf[:, :V])
         return buf.view(B, L, pitch)[:, :, :V]
