@@ -277,6 +277,73 @@ def run_gpu_arm(args, rank, world, local_rank):
         }))
 
 
+# ----------------------------------------------------------------------------- standalone kernel sweep
+def run_sweep(args):
+    """Single-kernel timings at the kernel-sweep shapes (fp16, seed 0): GEMM + bias + GELU with
+    M=153600, K=768, N=3072; LayerNorm and embedding on 153600 x 768; causal attention with B=512,
+    H=12, D=64, S in {300, 1024, 2048}.  --rows / --batch shrink the problem (for profiler captures).
+    One JSON line per kernel; not the headline metric."""
+    from gpt_triton_b200 import kernels as K
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, peak_kind = load_peaks()
+    g = torch.Generator().manual_seed(0)
+    M = args.rows or BATCH * SEQ
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        total = 0.0
+        for _ in range(args.steps):
+            flush.zero_()
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            total += s.elapsed_time(e)
+        return total / args.steps
+
+    def report(name, ms, bound, work, unit_peak, extra):
+        achieved = work / (ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+        print(json.dumps({"kernel": name, "ms": ms, "bound": bound, "achieved": achieved, "peak": unit_peak,
+                          "unit": "TFLOP/s" if bound == "tensor" else "GB/s", "frac": achieved / unit_peak,
+                          "peak_source": peak_kind, "l2": "flushed between timed launches", **extra}), flush=True)
+
+    which = args.sweep
+    if which in ("gemm", "all"):
+        x = torch.randn((M, 768), generator=g).half().to(dev)
+        w = (torch.randn((768, 3072), generator=g) * 0.02).half().to(dev)
+        b = torch.randn(3072, generator=g).half().to(dev)
+        pw = K.pack_weight(w)
+        out = torch.empty((M, 3072), device=dev, dtype=torch.float16)
+        ms = timed(lambda: K.fused_ffn(x, pw, bias=b, add_gelu=True, out=out))
+        report("gemm_bias_gelu", ms, "tensor", 2.0 * M * 768 * 3072, float(peaks["bf16_tflops"]), {"M": M, "K": 768, "N": 3072})
+        del x, out
+    if which in ("layernorm", "all"):
+        x = torch.randn((M, 768), generator=g).half().to(dev)
+        w, b = torch.ones(768, device=dev).half(), torch.zeros(768, device=dev).half()
+        ms = timed(lambda: K.fused_layer_norm(x, w, b))
+        report("layernorm", ms, "hbm", 2.0 * M * 768 * 2, float(peaks["hbm_gbs"]), {"M": M, "H": 768})
+    if which in ("embedding", "all"):
+        ids = torch.randint(0, 50257, (M // SEQ, SEQ), generator=g).to(dev)
+        wte = (torch.randn((50257, 768), generator=g) * 0.02).half().to(dev)
+        wpe = (torch.randn((1024, 768), generator=g) * 0.02).half().to(dev)
+        ms = timed(lambda: K.fused_embeddings(ids, wte, wpe))
+        report("embedding", ms, "hbm", 2.0 * ids.numel() * 768 * 2, float(peaks["hbm_gbs"]), {"tokens": ids.numel(), "H": 768})
+    if which in ("attention", "all"):
+        for S in (300, 1024, 2048):
+            B = args.batch or BATCH
+            qkv = (torch.randn((B, S, 3 * 768), generator=g) / 8).half().to(dev)
+            q, k, v = (t.view(B, S, 12, 64).transpose(1, 2) for t in qkv.split(768, dim=2))
+            ms = timed(lambda: K.flash_attention_v1(q, k, v, merged_heads=True))
+            report(f"attention_S{S}", ms, "tensor", 4.0 * B * 12 * 64 * S * (S + 1) / 2, float(peaks["bf16_tflops"]),
+                   {"B": B, "H": 12, "D": 64, "S": S, "hbm_gbs": 4.0 * B * S * 768 * 2 / (ms * 1e-3) / 1e9})
+            del qkv, q, k, v
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -284,7 +351,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", default=None, choices=["gemm", "layernorm", "embedding", "attention", "all"],
+                    help="time single kernels at the kernel-sweep shapes instead of the forward")
+    ap.add_argument("--rows", type=int, default=0, help="--sweep: rows (tokens) instead of 153600")
+    ap.add_argument("--batch", type=int, default=0, help="--sweep attention: batch instead of 512")
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
 
     rank = int(os.environ.get("RANK", "0"))

@@ -4,7 +4,7 @@
 // longest first.  Per CTA:
 //   warp 0      TMA producer: the 128x64 Q tile (double-buffered) and, per 64-key block, the K and
 //               V tiles (3-stage ring), all 128-byte swizzled, straight out of the strided q/k/v
-//               views (4-D tensor maps: head_dim, row, head, batch); no multicast
+//               views (4-D tensor maps: head_dim, row, head, batch); every CTA issues its own loads
 //   warp 1      tcgen05.mma issuer: S = Q K^T (128x64, fp32, tensor memory, double-buffered, issued
 //               one block ahead) and PV = P V (128x64, fresh accumulator per block, double-buffered)
 //   warps 2-5   softmax: one thread per query row.  Reads S from tensor memory, keeps the running

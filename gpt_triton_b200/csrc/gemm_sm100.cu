@@ -1,17 +1,28 @@
 // out[M,N] = [gelu](A[M,K] . B[N,K]^T + bias) + residual  on the 5th-generation tensor cores.
 //
-// Persistent, warp-specialised kernel, one CTA per SM:
-//   warp 0      TMA producer: 128x64 tile of A and 256x64 tile of B per stage, 128-byte swizzle,
-//               completion by mbarrier transaction bytes (no multicast anywhere)
+// Persistent, warp-specialised kernel, one CTA per SM.  Two variants of one template:
+//   CTAS = 1   a CTA computes a 128x256 tile alone (small problems)
+//   CTAS = 2   a cluster of two CTAs computes a 256x256 tile with tcgen05.mma.cta_group::2: each CTA stages
+//              its own 128 rows of A and its own 128-row half of the B tile, the even CTA issues the MMAs for
+//              both, each CTA drains its own 128 accumulator rows.  Halving the B bytes per CTA is what lets
+//              shared memory feed the tensor cores at full rate, and it buys a 6-deep instead of 4-deep ring.
+// Roles per CTA:
+//   warp 0      TMA producer: 128x64 tile of A and (256/CTAS)x64 tile of B per stage, 128-byte swizzle,
+//               completion by mbarrier transaction bytes; every CTA issues its own loads
 //   warp 1      allocates the 512 tensor-memory columns and issues tcgen05.mma (one thread);
 //               tcgen05.commit releases smem stages and publishes finished accumulators
 //   warps 2-9   epilogue: tcgen05.ld the 128x256 fp32 accumulator (one row per thread, each warp
-//               128 of the 256 columns), bias -> GELU -> residual -> cast -> global store.  The
-//               residual rows are fetched into registers and the bias into shared memory before
-//               the accumulator is awaited, so their latency hides behind the main loop.
+//               128 of the 256 columns), bias -> GELU -> residual -> cast.  16-bit results are staged
+//               in shared memory (128-byte swizzle) and leave as TMA tile stores of 32 rows x 64
+//               columns, which also clip the ragged M and N edges; fp32 or unaligned outputs are
+//               stored from registers.  The residual rows are fetched into registers and the bias
+//               into shared memory before the accumulator is awaited, so their latency hides behind
+//               the main loop.
 // Two 128x256 accumulators (2 x 256 columns) let the epilogue of tile i overlap the main
 // loop of tile i+1.  Every wait on an mbarrier is bounded; a wait that gives up raises a
 // CTA-wide abort flag, reports through status_word and the kernel drains and exits.
+#include <string.h>
+
 #include "sm100_primitives.cuh"
 
 namespace b200 {
@@ -23,19 +34,30 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
-constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr int B_STAGE_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 32 * (2 + NUM_EPI_WARPS);
 constexpr int EPI_COLS = BN / (NUM_EPI_WARPS / 4);  // columns per epilogue warp
 constexpr int EPI_CHUNKS = EPI_COLS / 32;
 constexpr int TMEM_COLS = 512;
-constexpr int GROUP_M = 16;  // row tiles per raster group (keeps a group's A rows and B columns L2-resident)
-constexpr int CTRL_BYTES = 256;  // mbarriers, tensor-memory base, abort flag
+constexpr int GROUP_ROWS = 2048;  // rows per raster group (keeps a group's A rows and B columns L2-resident)
+constexpr int CTRL_BYTES = 256;   // mbarriers, tensor-memory base, abort flag
 constexpr int BIAS_BYTES = 2 * BN * 4;  // bias of the current and the next tile, as fp32
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + CTRL_BYTES + BIAS_BYTES;
+constexpr int EPI_BOX_COLS = 64;        // TMA store box: 64 columns (128 bytes of 16-bit data) x 32 rows
+constexpr int EPI_WARP_STAGE_BYTES = 32 * EPI_BOX_COLS * 2;  // 4 KB per epilogue warp
+constexpr int EPI_STAGE_BYTES = NUM_EPI_WARPS * EPI_WARP_STAGE_BYTES;
+
+template <int CTAS>
+struct Cfg {
+  static constexpr int STAGES = CTAS == 1 ? 4 : 6;
+  static constexpr int TILE_M = BM * CTAS;  // rows per tile of the CTA group
+  static constexpr int B_ROWS = BN / CTAS;  // rows of the B tile this CTA stages
+  static constexpr int A_STAGE_BYTES = BM * BK * 2;
+  static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + CTRL_BYTES + BIAS_BYTES;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+  static constexpr int GROUP_M = GROUP_ROWS / TILE_M;
+};
 
 // Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 bytes, an
 // 8-row group is 1024 bytes (stride byte offset), leading byte offset unused for swizzled
@@ -49,17 +71,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;
   return d;
 }
-// Instruction descriptor for kind::f16: D fp32, A/B fp16 (0) or bf16 (1), both K-major, M=128, N=256.
-__host__ __device__ constexpr uint32_t make_idesc(int ab_format) {
+// Instruction descriptor for kind::f16: D fp32, A/B fp16 (0) or bf16 (1), both K-major, M = 128 (one CTA) or
+// 256 (CTA pair), N = 256.
+__host__ __device__ constexpr uint32_t make_idesc(int ab_format, int mma_m) {
   return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)(BN >> 3) << 17) |
-         ((uint32_t)(BM >> 4) << 24);
+         ((uint32_t)(mma_m >> 4) << 24);
 }
 
 struct TileCoord {
   int m, n;
 };
-// Raster: groups of GROUP_M row tiles; inside a group the row tile varies fastest, so the CTAs
+// Raster: groups of GROUP_M row tiles (GROUP_ROWS rows); inside a group the row tile varies fastest, so the CTAs
 // that run at the same time share a few B column tiles and GROUP_M A row tiles in L2.
+template <int GROUP_M>
 __device__ __forceinline__ TileCoord tile_coord(int64_t t, int m_tiles, int n_tiles) {
   const int64_t per_group = (int64_t)GROUP_M * n_tiles;
   const int group = (int)(t / per_group);
@@ -78,6 +102,7 @@ struct EpilogueArgs {
   const OutT* residual;
   OutT* out;
   int64_t ld_res, ld_out;
+  int tma_store;  // 16-bit output whose base and pitch allow a tensor map: results leave through TMA stores
 };
 
 // x * sigmoid(2y), y = sqrt(2/pi) (x + 0.044715 x^3): algebraically the reference's
@@ -97,6 +122,18 @@ __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&v)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
                "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
                : "memory");
+}
+
+// Tile store shared -> global through a tensor map; rows/columns outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's earlier bulk stores have finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 template <typename OutT>
@@ -131,11 +168,14 @@ struct ResidualRegs {
   uint4 v[EPI_COLS / 8];
 };
 
-// One thread, one row, 32 consecutive columns starting at col0: acc (+bias) -> GELU -> (+residual) -> store.
+// One thread, one row, 32 consecutive columns starting at col0: acc (+bias) -> GELU -> (+residual) -> out.
 // `bias_s` points at this chunk's 32 fp32 bias values in shared memory (zeros when there is no bias).
+// With `stage` != 0 (TMA-store path, 16-bit output) the 64 result bytes go to this thread's row of the warp's
+// staging tile at 16-byte slots [4*half, 4*half+4) (128-byte swizzle); otherwise they are stored to global memory.
 template <typename OutT, bool GELU>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const float* bias_s, const EpilogueArgs<OutT>& e,
-                                               const uint4* res_regs, int64_t row, int col0, int64_t N, int mode) {
+                                               const uint4* res_regs, int64_t row, int col0, int64_t N, int mode, uint32_t stage,
+                                               int half, int lane, bool row_ok) {
   float f[32];
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
@@ -149,10 +189,9 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = gelu_fast(f[j]);
   }
-  OutT* orow = e.out + row * e.ld_out + col0;
   const bool full = col0 + 32 <= N;
-  if (mode != STORE_SCALAR && full) {
-    if constexpr (sizeof(OutT) == 2) {
+  if constexpr (sizeof(OutT) == 2) {
+    if (stage != 0 || (mode != STORE_SCALAR && full)) {
       if (res_regs) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -164,18 +203,36 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
             f[g * 8 + 2 * j + 1] += r.y;
           }
         }
+      } else if (e.residual && row_ok) {
+        // ragged last column chunk on the staged path: element-wise, inside the matrix only
+        const OutT* rrow = e.residual + row * e.ld_res + col0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < N) f[j] += to_float(rrow[j]);
       }
       uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) w[j] = pack2<OutT>(f[2 * j], f[2 * j + 1]);
-      if (mode == STORE_32B) {
-        st_global_v8(orow, reinterpret_cast<const uint32_t(&)[8]>(w[0]));
-        st_global_v8(orow + 16, reinterpret_cast<const uint32_t(&)[8]>(w[8]));
-      } else {
+      if (stage != 0) {
+        const uint32_t rowaddr = stage + (uint32_t)lane * 128u;
+        const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll
-        for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+        for (int g = 0; g < 4; ++g) st_shared_v4(rowaddr + ((((uint32_t)(half * 4 + g)) ^ sw) << 4), w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+      } else {
+        OutT* orow = e.out + row * e.ld_out + col0;
+        if (mode == STORE_32B) {
+          st_global_v8(orow, reinterpret_cast<const uint32_t(&)[8]>(w[0]));
+          st_global_v8(orow + 16, reinterpret_cast<const uint32_t(&)[8]>(w[8]));
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+        }
       }
-    } else {
+      return;
+    }
+  } else {
+    if (mode != STORE_SCALAR && full) {
+      float* orow = reinterpret_cast<float*>(e.out) + row * e.ld_out + col0;
       if (e.residual) {
         const float* rrow = reinterpret_cast<const float*>(e.residual) + row * e.ld_res + col0;
 #pragma unroll
@@ -185,33 +242,42 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
         }
       }
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+      return;
     }
-  } else {
-    const OutT* rrow = e.residual ? e.residual + row * e.ld_res + col0 : nullptr;
+  }
+  // element-wise tail: ragged columns, unaligned output
+  OutT* orow = e.out + row * e.ld_out + col0;
+  const OutT* rrow = e.residual ? e.residual + row * e.ld_res + col0 : nullptr;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (col0 + j < N) {
-        float v = f[j];
-        if (rrow) v += to_float(rrow[j]);
-        orow[j] = from_float<OutT>(v);
-      }
+  for (int j = 0; j < 32; ++j) {
+    if (col0 + j < N) {
+      float v = f[j];
+      if (rrow) v += to_float(rrow[j]);
+      orow[j] = from_float<OutT>(v);
     }
   }
 }
 
-template <typename OutT, bool GELU>
+template <typename OutT, bool GELU, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, EpilogueArgs<OutT> epi,
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_out, EpilogueArgs<OutT> epi,
                int64_t M, int64_t N, int64_t K, uint32_t idesc, int* status_word) {
-  extern __shared__ uint8_t smem_raw[];
-  // 128-byte-swizzled tiles need 1024-byte aligned bases.
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* smem = smem_raw + (base - raw);
+  using C = Cfg<CTAS>;
+  constexpr int STAGES = C::STAGES;
+  // 128-byte-swizzled tiles need 1024-byte aligned bases (the dynamic shared memory base is the same in both
+  // CTAs of a pair, so the two CTAs use identical offsets, which cta_group::2 descriptors rely on).
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = smem_u32(smem);
+  if (base & 1023u) {  // never expected; refuse to run rather than compute on misplaced tiles (uniform over the grid)
+    if (threadIdx.x == 0 && status_word) atomicCAS(status_word, 0, 99);
+    return;
+  }
   const uint32_t smem_a = base;
-  const uint32_t smem_b = base + STAGES * A_STAGE_BYTES;
-  uint8_t* ctrl = smem + STAGES * STAGE_BYTES;
+  const uint32_t smem_b = base + STAGES * C::A_STAGE_BYTES;
+  const uint32_t smem_epi = base + STAGES * C::STAGE_BYTES;  // [NUM_EPI_WARPS][32 rows][128 bytes]
+  uint8_t* ctrl = smem + STAGES * C::STAGE_BYTES + EPI_STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);  // full[S], empty[S], acc_full[2], acc_empty[2], bias_ready[2]
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * STAGES;
@@ -225,8 +291,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;  // 0 = leader (issues the MMAs)
+  const int64_t group_id = CTAS == 2 ? (int64_t)(blockIdx.x >> 1) : (int64_t)blockIdx.x;
+  const int64_t num_groups = CTAS == 2 ? (int64_t)(gridDim.x >> 1) : (int64_t)gridDim.x;
 
-  const int m_tiles = (int)((M + BM - 1) / BM);
+  const int m_tiles = (int)((M + C::TILE_M - 1) / C::TILE_M);
   const int n_tiles = (int)((N + BN - 1) / BN);
   const int64_t num_tiles = (int64_t)m_tiles * n_tiles;
   const int num_kb = (int)((K + BK - 1) / BK);
@@ -238,7 +307,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_acc_full + 8 * a, 1);
-      mbar_init(bar_acc_empty + 8 * a, NUM_EPI_WARPS);
+      mbar_init(bar_acc_empty + 8 * a, NUM_EPI_WARPS * CTAS);  // the leader's barrier collects both CTAs' epilogue warps
       mbar_init(bar_bias + 8 * a, NUM_EPI_WARPS);
     }
     *abort_flag = 0;
@@ -246,11 +315,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CTAS == 2) {
+      tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // both CTAs' barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -260,16 +335,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int64_t t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
-        const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
+      // completion bytes of both CTAs' loads are posted on the leader's full barrier
+      const uint32_t full_base = CTAS == 2 ? mapa_shared(bar_full, 0) : bar_full;
+      for (int64_t t = group_id; t < num_tiles && alive; t += num_groups) {
+        const TileCoord tc = tile_coord<C::GROUP_M>(t, m_tiles, n_tiles);
+        const int row_a = tc.m * C::TILE_M + (int)cta_rank * BM;
+        const int row_b = tc.n * BN + (int)cta_rank * C::B_ROWS;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, status_word, 1)) {
             alive = false;
             break;
           }
-          mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
-          tma_load_2d(smem_a + stage * A_STAGE_BYTES, &map_a, bar_full + 8 * stage, kb * BK, tc.m * BM);
-          tma_load_2d(smem_b + stage * B_STAGE_BYTES, &map_b, bar_full + 8 * stage, kb * BK, tc.n * BN);
+          if constexpr (CTAS == 2) {
+            if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);
+            tma_load_2d_pair(smem_a + stage * C::A_STAGE_BYTES, &map_a, full_base + 8 * stage, kb * BK, row_a);
+            tma_load_2d_pair(smem_b + stage * C::B_STAGE_BYTES, &map_b, full_base + 8 * stage, kb * BK, row_b);
+          } else {
+            mbar_arrive_expect_tx(bar_full + 8 * stage, C::STAGE_BYTES);
+            tma_load_2d(smem_a + stage * C::A_STAGE_BYTES, &map_a, bar_full + 8 * stage, kb * BK, row_a);
+            tma_load_2d(smem_b + stage * C::B_STAGE_BYTES, &map_b, bar_full + 8 * stage, kb * BK, row_b);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -278,14 +363,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (the leader CTA's only, for a pair)
+    if (lane == 0 && cta_rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      for (int64_t t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      for (int64_t t = group_id; t < num_tiles && alive; t += num_groups) {
         if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, status_word, 2)) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
@@ -295,21 +380,24 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           tc_fence_after();
-          const uint64_t da = make_smem_desc(smem_a + stage * A_STAGE_BYTES);
-          const uint64_t db = make_smem_desc(smem_b + stage * B_STAGE_BYTES);
+          const uint64_t da = make_smem_desc(smem_a + stage * C::A_STAGE_BYTES);
+          const uint64_t db = make_smem_desc(smem_b + stage * C::B_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advance 16 elements (32 bytes) along K inside the swizzle row: +2 in 16-byte units
-            umma_f16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (uint32_t)((kb | k) != 0));
+            if constexpr (CTAS == 2)
+              umma_f16_pair(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (uint32_t)((kb | k) != 0));
+            else
+              umma_f16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (uint32_t)((kb | k) != 0));
           }
-          umma_commit(bar_empty + 8 * stage);
+          if constexpr (CTAS == 2) umma_commit_pair(bar_empty + 8 * stage); else umma_commit(bar_empty + 8 * stage);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!alive) break;
-        umma_commit(bar_acc_full + 8 * acc);
+        if constexpr (CTAS == 2) umma_commit_pair(bar_acc_full + 8 * acc); else umma_commit(bar_acc_full + 8 * acc);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
@@ -328,9 +416,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uintptr_t res_al = epi.residual ? (reinterpret_cast<uintptr_t>(epi.residual) | (uintptr_t)(epi.ld_res * esz)) : 0;
     int mode = STORE_SCALAR;
     if (((out_al | res_al) & 15) == 0) mode = (esz == 2 && (out_al & 31) == 0) ? STORE_32B : STORE_16B;
-    for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const TileCoord tc = tile_coord(t, m_tiles, n_tiles);
-      const int64_t row = (int64_t)tc.m * BM + quarter * 32 + lane;
+    const uint32_t acc_empty_base = CTAS == 2 ? mapa_shared(bar_acc_empty, 0) : bar_acc_empty;
+    const bool use_tma = esz == 2 && epi.tma_store != 0;
+    const uint32_t stage_addr = use_tma ? smem_epi + (uint32_t)(warp - 2) * EPI_WARP_STAGE_BYTES : 0u;
+    for (int64_t t = group_id; t < num_tiles; t += num_groups) {
+      const TileCoord tc = tile_coord<C::GROUP_M>(t, m_tiles, n_tiles);
+      const int64_t row = (int64_t)tc.m * C::TILE_M + (int64_t)cta_rank * BM + quarter * 32 + lane;
       const int col_base = tc.n * BN + col_half * EPI_COLS;
       const bool row_ok = row < M;
       // Prefetch what does not depend on the accumulator: bias -> shared memory, residual -> registers.
@@ -355,6 +446,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, status_word, 4)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_half * EPI_COLS);
+      const int row_warp = (int)(tc.m * C::TILE_M + (int)cta_rank * BM + quarter * 32);  // first row of this warp's 32
 #pragma unroll
       for (int c = 0; c < EPI_CHUNKS; ++c) {
         uint32_t v[32];
@@ -364,17 +456,40 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // accumulator fully read: hand it back to the MMA warp before doing the last chunk's math
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+          if (lane == 0) {
+            if constexpr (CTAS == 2) mbar_arrive_cluster(acc_empty_base + 8 * acc); else mbar_arrive(bar_acc_empty + 8 * acc);
+          }
         }
         const int col0 = col_base + c * 32;
-        if (row_ok && col0 < N)
-          epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, res_in_regs ? &res.v[c * 4] : nullptr, row, col0, N, mode);
+        if (use_tma) {
+          if ((c & 1) == 0) {
+            // the staging tile is about to be overwritten: the previous TMA store must be done reading it
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+          }
+          if (col0 < N)
+            epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode,
+                                       stage_addr, c & 1, lane, row_ok);
+          if ((c & 1) == 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            const int box_col = col_base + (c >> 1) * EPI_BOX_COLS;
+            if (lane == 0 && box_col < N && row_warp < M) {
+              tma_store_2d(&map_out, stage_addr, box_col, row_warp);
+              tma_store_commit();
+            }
+          }
+        } else if (row_ok && col0 < N) {
+          epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode, 0u,
+                                     0, lane, row_ok);
+        }
       }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
       }
     }
+    if (use_tma && lane == 0) tma_store_wait_read();  // staging memory must outlive the last bulk store's read
   }
 
   // ------------------------------------------------------------ teardown
@@ -387,9 +502,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the peer may still be signalling this CTA's barriers or reading its tiles
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (CTAS == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -408,24 +524,97 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t col
   return r == CUDA_SUCCESS ? B200_OK : B200_ERR_CUDA;
 }
 
+// Largest number of 2-CTA clusters of this kernel that can be resident at once (cached per instantiation).
 template <typename OutT, bool GELU>
-static int launch_typed(const CUtensorMap& ma, const CUtensorMap& mb, const void* bias, const void* residual, void* out,
-                        int64_t M, int64_t N, int64_t K, int64_t ld_res, int64_t ld_out, int op_dtype, int* status_word,
-                        cudaStream_t stream) {
+static int max_pairs() {
+  static int cached = -1;
+  if (cached >= 0) return cached;
+  if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES) != cudaSuccess) {
+    cudaGetLastError();
+    return cached = 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)sm_count() / 2 * 2);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = Cfg<2>::SMEM_BYTES;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tn_kernel<OutT, GELU, 2>, &cfg) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    n = 0;
+  }
+  cached = n;
+  return n;
+}
+
+// Map over the 16-bit output [M, N] (pitch ld_out) for tile stores of 64 columns x 32 rows.
+static int make_out_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N, int64_t ld_out, int io_dtype) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return B200_ERR_CUDA;
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_out * 2};
+  cuuint32_t box[2] = {(cuuint32_t)EPI_BOX_COLS, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, io_dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ptr, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_CUDA;
+}
+
+template <typename OutT, bool GELU, int CTAS>
+static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const EpilogueArgs<OutT>& epi, int64_t M, int64_t N, int64_t K,
+                          int op_dtype, int64_t groups, int* status_word, cudaStream_t stream) {
+  using C = Cfg<CTAS>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return B200_ERR_CUDA;
+    if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return B200_ERR_CUDA;
     attr_set = true;
   }
-  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out};
-  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int64_t grid = sm_count();
-  if (grid > tiles) grid = tiles;
-  gemm_tn_kernel<OutT, GELU><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, epi, M, N, K, make_idesc(op_dtype == B200_BF16 ? 1 : 0),
-                                                                                 status_word);
+  const uint32_t idesc = make_idesc(op_dtype == B200_BF16 ? 1 : 0, BM * CTAS);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(groups * CTAS));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = CTAS, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tn_kernel<OutT, GELU, CTAS>, ma, mb, mo, epi, M, N, K, idesc, status_word);
   note_launches(1);
-  return status_from_cuda(cudaGetLastError());
+  return status_from_cuda(e);
+}
+
+template <typename OutT, bool GELU>
+static int launch_typed(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K,
+                        int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int* status_word, cudaStream_t stream) {
+  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0};
+  CUtensorMap mo;
+  memset(&mo, 0, sizeof(mo));
+  if (sizeof(OutT) == 2 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_out % 8 == 0 &&
+      make_out_map(&mo, out, M, N, ld_out, DType<OutT>::code) == B200_OK)
+    epi.tma_store = 1;
+  const int64_t n_tiles = (N + BN - 1) / BN;
+  const int pairs = M > BM ? max_pairs<OutT, GELU>() : 0;
+  CUtensorMap ma, mb;
+  int st = make_map(&ma, a, M, K, lda, BM, op_dtype);
+  if (st != B200_OK) return st;
+  if (pairs > 0) {
+    st = make_map(&mb, b, N, K, ldb, Cfg<2>::B_ROWS, op_dtype);
+    if (st != B200_OK) return st;
+    const int64_t tiles = ((M + Cfg<2>::TILE_M - 1) / Cfg<2>::TILE_M) * n_tiles;
+    return launch_variant<OutT, GELU, 2>(ma, mb, mo, epi, M, N, K, op_dtype, tiles < pairs ? tiles : pairs, status_word, stream);
+  }
+  st = make_map(&mb, b, N, K, ldb, Cfg<1>::B_ROWS, op_dtype);
+  if (st != B200_OK) return st;
+  const int64_t tiles = ((M + BM - 1) / BM) * n_tiles;
+  const int64_t sms = sm_count();
+  return launch_variant<OutT, GELU, 1>(ma, mb, mo, epi, M, N, K, op_dtype, tiles < sms ? tiles : sms, status_word, stream);
 }
 
 }  // namespace gemm
@@ -441,15 +630,10 @@ int launch_gemm(const void* a, const void* b, const void* bias, const void* resi
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || lda % 8 || ldb % 8 || lda < K || ldb < K)
     return B200_ERR_ALIGNMENT;
   if (ld_out < N || (residual && ld_res < N)) return B200_ERR_BAD_ARGUMENT;
-  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_BAD_ARGUMENT;
-  CUtensorMap ma, mb;
-  int st = make_map(&ma, a, M, K, lda, BM, op_dtype);
-  if (st != B200_OK) return st;
-  st = make_map(&mb, b, N, K, ldb, BN, op_dtype);
-  if (st != B200_OK) return st;
-#define B200_GEMM_DISPATCH(T)                                                                                               \
-  return add_gelu ? launch_typed<T, true>(ma, mb, bias, residual, out, M, N, K, ld_res, ld_out, op_dtype, status_word, stream) \
-                  : launch_typed<T, false>(ma, mb, bias, residual, out, M, N, K, ld_res, ld_out, op_dtype, status_word, stream)
+  if (M > 0x7fffffffLL - 256 || N > 0x7fffffffLL - 256 || K > 0x7fffffffLL - 64) return B200_ERR_BAD_ARGUMENT;
+#define B200_GEMM_DISPATCH(T)                                                                                                           \
+  return add_gelu ? launch_typed<T, true>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, status_word, stream) \
+                  : launch_typed<T, false>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, status_word, stream)
   switch (io_dtype) {
     case B200_F32: B200_GEMM_DISPATCH(float);
     case B200_F16: B200_GEMM_DISPATCH(__half);

@@ -280,8 +280,15 @@ def test_qkv_split_views_and_merged_heads():
     for a, b in ((q, g["q"]), (kk, g["k"]), (v, g["v"])):
         assert a.shape == b.shape
         assert_close(a.contiguous(), b, scale_big=False)
-    # attention straight from the strided views; merged-head output equals transpose+reshape
-    ref = orc.flash_attention_v1(g["q"], g["k"], g["v"])
+    # attention straight from such strided views (head size 16, fp32); merged-head output equals transpose+reshape
+    gen = torch.Generator().manual_seed(21)
+    x = torch.randn((2, 70, 64), generator=gen)
+    w = 0.2 * torch.randn((64, 192), generator=gen)
+    b = 0.1 * torch.randn(192, generator=gen)
+    q, kk, v = k.matmul_and_split_qkv(cu(x), cu(w), cu(b), 4)
+    assert not q.is_contiguous() and q.shape == (2, 4, 70, 16)
+    # same q, k, v on both sides: differences in the projection's last bit would otherwise flip fp16 operand roundings
+    ref = orc.flash_attention_v1(q.cpu().contiguous(), kk.cpu().contiguous(), v.cpu().contiguous())
     assert_close(k.flash_attention_v1(q, kk, v), ref, scale_big=False, floor=ATTN_TOL)
     merged = k.flash_attention_v1(q, kk, v, merged_heads=True)
     B, N, L, H = ref.shape
