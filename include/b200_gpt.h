@@ -102,6 +102,27 @@ int b200_ffn(const void* x, const void* w, const void* bias, const void* residua
              int* status_word, void* stream);
 
 /*
+ * b200_ffn for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * operators allocate freely through torch).  Examples: a serving runtime that has given all free HBM
+ * to its own pool, or an enqueue-style plugin callback where cudaMalloc and the device-wide
+ * synchronisation it implies are not allowed.  Same arguments and results as b200_ffn minus the
+ * workspace: the packed operands go to an array of B200_FFN_STATIC_SCRATCH_BYTES that is part of the
+ * library image on every GPU that loads it (held until the process exits).  The call makes no
+ * cudaMalloc/cudaFree or other allocating call.
+ *  - Limit: if the operands, both packed (b200_ffn_workspace_bytes(M, N, K, 0, B200_F32) bytes),
+ *    exceed B200_FFN_STATIC_SCRATCH_BYTES the call returns B200_ERR_WORKSPACE and launches nothing.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current); make that first call outside any stream capture.
+ *  - Every call on a device shares the one array, which keeps the previous call's contents (nothing
+ *    needs clearing: each call overwrites what it reads).  Two calls that may overlap on the GPU
+ *    (different streams) race on it; serialise them.
+ */
+#define B200_FFN_STATIC_SCRATCH_BYTES (32u << 20)
+int b200_ffn_static_scratch(const void* x, const void* w, const void* bias, const void* residual, void* out, int64_t M,
+                            int64_t N, int64_t K, int64_t ld_out, int w_is_nk, int add_gelu, int dtype, int* status_word,
+                            void* stream);
+
+/*
  * Causal attention with online softmax over 64-key blocks, fp16 operands, fp32
  * statistics: stands in for flash_attention_v1 (kernels.py:478-525; kernel
  * kernels.py:375-474).  q, k, v, out are addressed as base + b*s[0] + h*s[1] + l*s[2] + d
