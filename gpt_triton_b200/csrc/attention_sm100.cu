@@ -264,6 +264,8 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
       const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
       const int row = it.q0 + r_in_tile;
+      const int warp_row0 = it.q0 + quarter * 32;       // first query row of this warp
+      const bool warp_live = warp_row0 < p.L;           // a warp whose 32 rows all lie beyond L only keeps the handshakes going
       float o[D];
 #pragma unroll
       for (int i = 0; i < D; ++i) o[i] = 0.f;
@@ -278,10 +280,13 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t s_addr = tmem_s + lane_addr + sb * BLOCK_N;
         const int k0 = j * BLOCK_N;
         const bool need_mask = k0 + BLOCK_N - 1 > it.q0;  // some key of this block lies above some row's diagonal
+        // a 32-key chunk whose first key lies above this warp's last row is masked for the whole warp
+        const int live_chunks = (!warp_live || k0 > warp_row0 + 31) ? 0 : (k0 + 32 > warp_row0 + 31 ? 1 : 2);
         // pass 1: block maximum of the raw scores (the scale is positive, so it commutes with max)
         float bm = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
+          if (c >= live_chunks) break;
           uint32_t v[32];
           tmem_ld_32x32(s_addr + c * 32, v);
           tmem_ld_wait();
@@ -304,6 +309,14 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         float psum = 0.f;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
+          if (c >= live_chunks) {
+            // masked for every row of the warp: P = 0 (rows beyond L may keep whatever is there: nothing reads their output)
+            if (warp_live) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) st_shared_v4(p_row + ((((uint32_t)(c * 4 + g)) ^ sw) << 4), 0u, 0u, 0u, 0u);
+            }
+            continue;
+          }
           uint32_t v[32];
           tmem_ld_32x32(s_addr + c * 32, v);
           tmem_ld_wait();
@@ -344,13 +357,15 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             break;
           }
           tc_fence_after();
+          if (warp_live) {
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_pv + lane_addr + ob * D + c * 32, v);
-            tmem_ld_wait();
+            for (int c = 0; c < 2; ++c) {
+              uint32_t v[32];
+              tmem_ld_32x32(tmem_pv + lane_addr + ob * D + c * 32, v);
+              tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], mult_prev, __uint_as_float(v[i]));
+              for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], mult_prev, __uint_as_float(v[i]));
+            }
           }
           tc_fence_before();
           __syncwarp();
@@ -364,13 +379,15 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t ob = (it_count - 1) & 1;
         if (!mbar_wait(bar_pv_full + 8 * ob, ((it_count - 1) >> 1) & 1, abort_flag, p.status_word, 21)) break;
         tc_fence_after();
+        if (warp_live) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_pv + lane_addr + ob * D + c * 32, v);
-          tmem_ld_wait();
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_pv + lane_addr + ob * D + c * 32, v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], mult_prev, __uint_as_float(v[i]));
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], mult_prev, __uint_as_float(v[i]));
+          }
         }
         tc_fence_before();
         __syncwarp();
