@@ -193,7 +193,7 @@ def run_gpu_arm(args, rank, world, local_rank):
     def e2e_step():
         nonlocal gathered
         x = ids_host.to(dev, non_blocking=True)
-        am = model.logits(x).argmax(dim=-1)
+        am = model.logits_and_next_ids(x)[1]  # argmax fused into the lm_head epilogue
         if world > 1:
             parts = [torch.empty_like(am) for _ in range(world)]
             dist.all_gather(parts, am)  # 8 bytes per token cross NVLink

@@ -96,6 +96,12 @@ __device__ __forceinline__ TileCoord tile_coord(int64_t t, int m_tiles, int n_ti
   return c;
 }
 
+struct ArgmaxPartials {
+  float* val;
+  int* idx;
+  int64_t ld;
+};
+
 template <typename OutT>
 struct EpilogueArgs {
   const OutT* bias;
@@ -103,6 +109,11 @@ struct EpilogueArgs {
   OutT* out;
   int64_t ld_res, ld_out;
   int tma_store;  // 16-bit output whose base and pitch allow a tensor map: results leave through TMA stores
+  // Optional row-argmax partials: for every row, the maximum of each 128-column slice of the (rounded) output
+  // and its column, stored slice-major: amax_val[slice * amax_ld + row].  NULL = not requested.
+  float* amax_val;
+  int* amax_idx;
+  int64_t amax_ld;
 };
 
 // x * sigmoid(2y), y = sqrt(2/pi) (x + 0.044715 x^3): algebraically the reference's
@@ -130,6 +141,11 @@ __device__ __forceinline__ float gelu_tanh_approx(float x) {
   return fmaf(h, t, h);
 }
 
+__device__ __forceinline__ void ld_global_v8(const void* p, uint4& a, uint4& b) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+               : "l"(p));
+}
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&v)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
                "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
@@ -187,7 +203,7 @@ struct ResidualRegs {
 template <typename OutT, bool GELU>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const float* bias_s, const EpilogueArgs<OutT>& e,
                                                const uint4* res_regs, int64_t row, int col0, int64_t N, int mode, uint32_t stage,
-                                               int half, int lane, bool row_ok) {
+                                               int half, int lane, bool row_ok, float& best_val, int& best_idx) {
   float f[32];
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
@@ -225,6 +241,15 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
       uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) w[j] = pack2<OutT>(f[2 * j], f[2 * j + 1]);
+      if (e.amax_val) {
+        // compare what is stored (the rounded values); strict '>' keeps the lowest column among equal maxima
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 r = unpack2<OutT>(w[j]);
+          if (col0 + 2 * j < N && r.x > best_val) best_val = r.x, best_idx = col0 + 2 * j;
+          if (col0 + 2 * j + 1 < N && r.y > best_val) best_val = r.y, best_idx = col0 + 2 * j + 1;
+        }
+      }
       if (stage != 0) {
         const uint32_t rowaddr = stage + (uint32_t)lane * 128u;
         const uint32_t sw = (uint32_t)(lane & 7);
@@ -255,6 +280,11 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
       }
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+      if (e.amax_val) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (f[j] > best_val) best_val = f[j], best_idx = col0 + j;
+      }
       return;
     }
   }
@@ -266,7 +296,9 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
     if (col0 + j < N) {
       float v = f[j];
       if (rrow) v += to_float(rrow[j]);
-      orow[j] = from_float<OutT>(v);
+      const OutT o = from_float<OutT>(v);
+      orow[j] = o;
+      if (e.amax_val && to_float(o) > best_val) best_val = to_float(o), best_idx = col0 + j;
     }
   }
 }
@@ -446,9 +478,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool res_in_regs = esz == 2 && epi.residual && mode != STORE_SCALAR && row_ok;
       if (res_in_regs) {
         const OutT* rrow = epi.residual + row * epi.ld_res + col_base;
+        if ((res_al & 31) == 0) {
+          // 32-byte loads: every request is a whole sector
 #pragma unroll
-        for (int i = 0; i < EPI_COLS / 8; ++i) {
-          if (col_base + (i / 4) * 32 + 32 <= N) res.v[i] = *reinterpret_cast<const uint4*>(rrow + i * 8);
+          for (int i = 0; i < EPI_COLS / 8; i += 2) {
+            if (col_base + (i / 4) * 32 + 32 <= N) ld_global_v8(rrow + i * 8, res.v[i], res.v[i + 1]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < EPI_COLS / 8; ++i) {
+            if (col_base + (i / 4) * 32 + 32 <= N) res.v[i] = *reinterpret_cast<const uint4*>(rrow + i * 8);
+          }
         }
       }
       // bias visible to all epilogue warps (an mbarrier, not bar.sync: its wait is bounded like every other)
@@ -459,6 +499,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_half * EPI_COLS);
       const int row_warp = (int)(tc.m * C::TILE_M + (int)cta_rank * BM + quarter * 32);  // first row of this warp's 32
+      float best_val = -INFINITY;
+      int best_idx = 0;
 #pragma unroll
       for (int c = 0; c < EPI_CHUNKS; ++c) {
         uint32_t v[32];
@@ -481,7 +523,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           if (col0 < N)
             epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode,
-                                       stage_addr, c & 1, lane, row_ok);
+                                       stage_addr, c & 1, lane, row_ok, best_val, best_idx);
           if ((c & 1) == 1) {
             fence_proxy_async_smem();
             __syncwarp();
@@ -493,8 +535,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         } else if (row_ok && col0 < N) {
           epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode, 0u,
-                                     0, lane, row_ok);
+                                     0, lane, row_ok, best_val, best_idx);
         }
+      }
+      if (epi.amax_val && row_ok) {
+        const int64_t slice = (int64_t)tc.n * (BN / EPI_COLS) + col_half;
+        epi.amax_val[slice * epi.amax_ld + row] = best_val;
+        epi.amax_idx[slice * epi.amax_ld + row] = best_idx;
       }
       if (++acc == 2) {
         acc = 0;
@@ -604,8 +651,9 @@ static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CU
 
 template <typename OutT, bool GELU>
 static int launch_typed(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K,
-                        int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int* status_word, cudaStream_t stream) {
-  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0};
+                        int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, const ArgmaxPartials& am, int* status_word,
+                        cudaStream_t stream) {
+  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.ld};
   CUtensorMap mo;
   memset(&mo, 0, sizeof(mo));
   if (sizeof(OutT) == 2 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_out % 8 == 0 &&
@@ -631,10 +679,48 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
 
 }  // namespace gemm
 
+// Row argmax from the per-slice partials the GEMM epilogue wrote: one thread per row walks the slices in column
+// order; strict '>' keeps the lowest column among equal maxima.
+__global__ void __launch_bounds__(256)
+argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx, int64_t ld, int slices, int64_t M, int64_t* __restrict__ out) {
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float best = -INFINITY;
+  int where = 0;
+  for (int s = 0; s < slices; ++s) {
+    const float v = val[(int64_t)s * ld + row];
+    if (v > best) best = v, where = idx[(int64_t)s * ld + row];
+  }
+  out[row] = where;
+}
+
 int launch_gemm(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                 int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
                 int add_gelu, int* status_word, cudaStream_t stream) {
+  return launch_gemm_argmax(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, io_dtype, add_gelu, nullptr, nullptr, 0,
+                            status_word, stream);
+}
+
+size_t gemm_argmax_workspace_bytes(int64_t M, int64_t N) {
+  if (M <= 0 || N <= 0) return 0;
+  const int64_t slices = (N + gemm::BN - 1) / gemm::BN * (gemm::BN / gemm::EPI_COLS);
+  const int64_t ld = (M + 63) / 64 * 64;
+  return (size_t)(slices * ld) * 8;
+}
+
+int launch_gemm_argmax(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                       int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
+                       int add_gelu, int64_t* argmax_out, void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream) {
   using namespace gemm;
+  ArgmaxPartials am{nullptr, nullptr, 0};
+  if (argmax_out) {
+    const size_t need = gemm_argmax_workspace_bytes(M, N);
+    if (need > 0 && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))) return B200_ERR_WORKSPACE;
+    am.ld = (M + 63) / 64 * 64;
+    const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
+    am.val = static_cast<float*>(workspace);
+    am.idx = reinterpret_cast<int*>(am.val + slices * am.ld);
+  }
   if (M == 0 || N == 0) return B200_OK;
   if (K < 1 || M < 0 || N < 0) return B200_ERR_BAD_ARGUMENT;
   if (op_dtype != B200_F16 && op_dtype != B200_BF16) return B200_ERR_BAD_ARGUMENT;
@@ -643,16 +729,21 @@ int launch_gemm(const void* a, const void* b, const void* bias, const void* resi
     return B200_ERR_ALIGNMENT;
   if (ld_out < N || (residual && ld_res < N)) return B200_ERR_BAD_ARGUMENT;
   if (M > 0x7fffffffLL - 256 || N > 0x7fffffffLL - 256 || K > 0x7fffffffLL - 64) return B200_ERR_BAD_ARGUMENT;
-#define B200_GEMM_DISPATCH(T)                                                                                                           \
-  return add_gelu ? launch_typed<T, true>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, status_word, stream) \
-                  : launch_typed<T, false>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, status_word, stream)
+  int st = B200_ERR_BAD_ARGUMENT;
+#define B200_GEMM_DISPATCH(T)                                                                                                              \
+  st = add_gelu ? launch_typed<T, true>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, am, status_word, stream) \
+                : launch_typed<T, false>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, am, status_word, stream)
   switch (io_dtype) {
-    case B200_F32: B200_GEMM_DISPATCH(float);
-    case B200_F16: B200_GEMM_DISPATCH(__half);
-    case B200_BF16: B200_GEMM_DISPATCH(__nv_bfloat16);
+    case B200_F32: B200_GEMM_DISPATCH(float); break;
+    case B200_F16: B200_GEMM_DISPATCH(__half); break;
+    case B200_BF16: B200_GEMM_DISPATCH(__nv_bfloat16); break;
   }
 #undef B200_GEMM_DISPATCH
-  return B200_ERR_BAD_ARGUMENT;
+  if (st != B200_OK || !argmax_out) return st;
+  const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
+  argmax_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(am.val, am.idx, am.ld, (int)slices, M, argmax_out);
+  note_launches(1);
+  return status_from_cuda(cudaGetLastError());
 }
 
 }  // namespace b200

@@ -151,22 +151,34 @@ class FusedGPT(_EvalOnly):
         return K.fused_layer_norm(y, self.layer_norm_weight.data, self.layer_norm_bias.data)
 
     @torch.no_grad()
-    def lm_head(self, hidden):
+    def lm_head(self, hidden, return_argmax=False):
         """hidden (batch, seqlen, n_embd) -> logits (batch, seqlen, vocab_size) with the tied
         embedding matrix.  The logits buffer's row pitch is padded to a multiple of 64 elements so
         every row starts 128-byte aligned (wide stores); the result is the [..., :vocab_size] view
-        of it."""
+        of it.  ``return_argmax=True`` also returns the greedy next-token ids (batch, seqlen), taken
+        in the GEMM's epilogue (16-bit models)."""
         B, L, h = hidden.shape
         V = self.config.vocab_size
         pitch = (V + 63) // 64 * 64
         buf = torch.empty((B * L, pitch), device=hidden.device, dtype=hidden.dtype)
-        K.fused_ffn(hidden.reshape(B * L, h), self._operand(self.wte_weight, weight_is_nk=True), out=buf[:, :V])
-        return buf.view(B, L, pitch)[:, :, :V]
+        w = self._operand(self.wte_weight, weight_is_nk=True)
+        if return_argmax and hidden.dtype != torch.float32:
+            _, ids = K.fused_ffn(hidden.reshape(B * L, h), w, out=buf[:, :V], return_argmax=True)
+            return buf.view(B, L, pitch)[:, :, :V], ids.view(B, L)
+        K.fused_ffn(hidden.reshape(B * L, h), w, out=buf[:, :V])
+        logits = buf.view(B, L, pitch)[:, :, :V]
+        return (logits, logits.argmax(dim=-1)) if return_argmax else logits
 
     @torch.no_grad()
     def logits(self, x):
         """ids -> logits: forward() followed by the tied lm_head."""
         return self.lm_head(self.forward(x))
+
+    @torch.no_grad()
+    def logits_and_next_ids(self, x):
+        """ids -> (logits, greedy next-token ids): forward(), then the tied lm_head with the argmax fused
+        into its epilogue."""
+        return self.lm_head(self.forward(x), return_argmax=True)
 
     def get_fwd_flops(self, num_tokens):
         """The reference's analytic count (gpt.py:182-196): embeddings counted as matmuls,

@@ -202,6 +202,34 @@ def test_ffn_weight_layouts_and_packed():
     assert buf2[:, 1001:].abs().max().item() == 0
 
 
+def _first_argmax(z):
+    """Lowest column holding the row maximum (what the fused argmax promises)."""
+    zf = z.float().cpu()
+    is_max = zf == zf.max(dim=1, keepdim=True).values
+    cols = torch.arange(zf.shape[1]).expand_as(zf)
+    return torch.where(is_max, cols, torch.full_like(cols, zf.shape[1])).min(dim=1).values
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K_", [(300, 1001, 128), (1, 8, 8), (1000, 50257, 64), (129, 256, 72)])
+def test_ffn_fused_argmax(M, N, K_, dtype):
+    """Row argmax out of the GEMM epilogue == first-occurrence argmax of the stored output, including
+    ragged N, many column slices (vocabulary-sized N) and rows full of ties (coarse values)."""
+    k = K()
+    g = torch.Generator().manual_seed(M + N)
+    x = (torch.randn((M, K_), generator=g) * 0.5).to(dtype)
+    w = torch.randint(-2, 3, (N, K_), generator=g).to(dtype) * 0.25  # coarse weights -> many exact ties
+    pw = k.pack_weight(cu(w), weight_is_nk=True)
+    pitch = (N + 63) // 64 * 64
+    buf = torch.zeros((M, pitch), device=DEV, dtype=dtype)
+    z, ids = k.fused_ffn(cu(x), pw, out=buf[:, :N], return_argmax=True)
+    assert ids.shape == (M,) and ids.dtype == torch.int64
+    assert_close(z, orc.fused_ffn(x, w.T.contiguous()))
+    assert torch.equal(ids.cpu(), _first_argmax(z))
+    plain = k.fused_ffn(cu(x), pw)
+    assert torch.equal(plain, z)  # asking for the argmax does not change the output
+
+
 def test_ffn_full_size_fp16_gelu():
     """The kernel-sweep GEMM: M=153600, K=768, N=3072, fp16, bias + GELU.  Oracle parity on a row
     sample, and row independence: the same rows computed as a small problem give the same bits."""

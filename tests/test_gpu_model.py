@@ -112,9 +112,15 @@ def test_gpt2_small_fp16_vs_oracle_and_batch_independence():
     _argmax_agrees_where_clear(small_logits, ref_logits, 2e-2)
     full_hidden = model(ids.to(DEV))
     assert torch.equal(full_hidden[sel.to(DEV)], small_hidden)
-    full_logits = model.lm_head(full_hidden)
-    assert full_logits.shape == (512, 300, 50257)
+    full_logits, next_ids = model.lm_head(full_hidden, return_argmax=True)
+    assert full_logits.shape == (512, 300, 50257) and next_ids.shape == (512, 300)
     assert torch.equal(full_logits[sel.to(DEV)].cpu(), small_logits)
+    # fused argmax: picks a maximum of every row, and the first one (checked on the sampled sequences)
+    picked = full_logits.gather(2, next_ids[..., None])[..., 0]
+    assert torch.equal(picked, full_logits.max(dim=-1).values)
+    sl = small_logits.float()
+    first = torch.where(sl == sl.max(-1, keepdim=True).values, torch.arange(50257).expand_as(sl), torch.full(sl.shape, 50257)).min(-1).values
+    assert torch.equal(next_ids[sel.to(DEV)].cpu(), first)
 
 
 def test_training_mode_rejected():
