@@ -5,19 +5,19 @@
 //   CTAS = 2   a cluster of two CTAs computes a 256x256 tile with tcgen05.mma.cta_group::2: each CTA stages
 //              its own 128 rows of A and its own 128-row half of the B tile, the even CTA issues the MMAs for
 //              both, each CTA drains its own 128 accumulator rows.  Halving the B bytes per CTA is what lets
-//              shared memory feed the tensor cores at full rate, and it buys a 6-deep instead of 4-deep ring.
+//              shared memory feed the tensor cores at full rate, and it buys a 5-deep instead of 3-deep ring.
 // Roles per CTA:
 //   warp 0      TMA producer: 128x64 tile of A and (256/CTAS)x64 tile of B per stage, 128-byte swizzle,
 //               completion by mbarrier transaction bytes; every CTA issues its own loads
 //   warp 1      allocates the 512 tensor-memory columns and issues tcgen05.mma (one thread);
 //               tcgen05.commit releases smem stages and publishes finished accumulators
 //   warps 2-9   epilogue: tcgen05.ld the 128x256 fp32 accumulator (one row per thread, each warp
-//               128 of the 256 columns), bias -> GELU -> residual -> cast.  16-bit results are staged
-//               in shared memory (128-byte swizzle) and leave as TMA tile stores of 32 rows x 64
-//               columns, which also clip the ragged M and N edges; fp32 or unaligned outputs are
-//               stored from registers.  The residual rows are fetched into registers and the bias
-//               into shared memory before the accumulator is awaited, so their latency hides behind
-//               the main loop.
+//               128 of the 256 columns), bias -> GELU -> residual -> cast.  For 16-bit data each warp
+//               owns two 32-row x 64-column staging boxes in shared memory (128-byte swizzle): the
+//               residual tile is TMA-loaded into them before the accumulator is awaited, results
+//               overwrite it in place and leave as TMA tile stores, which also clip the ragged M and N
+//               edges.  fp32 or unaligned outputs are stored from registers (residual prefetched into
+//               registers).  The bias goes to shared memory ahead of the accumulator as well.
 // Two 128x256 accumulators (2 x 256 columns) let the epilogue of tile i overlap the main
 // loop of tile i+1.  Every wait on an mbarrier is bounded; a wait that gives up raises a
 // CTA-wide abort flag, reports through status_word and the kernel drains and exits.
@@ -43,12 +43,13 @@ constexpr int GROUP_ROWS = 2048;  // rows per raster group (keeps a group's A ro
 constexpr int CTRL_BYTES = 256;   // mbarriers, tensor-memory base, abort flag
 constexpr int BIAS_BYTES = 2 * BN * 4;  // bias of the current and the next tile, as fp32
 constexpr int EPI_BOX_COLS = 64;        // TMA store box: 64 columns (128 bytes of 16-bit data) x 32 rows
-constexpr int EPI_WARP_STAGE_BYTES = 32 * EPI_BOX_COLS * 2;  // 4 KB per epilogue warp
+constexpr int EPI_BOX_BYTES = 32 * EPI_BOX_COLS * 2;        // 4 KB
+constexpr int EPI_WARP_STAGE_BYTES = (EPI_COLS / EPI_BOX_COLS) * EPI_BOX_BYTES;  // one box per 64 of the warp's 128 columns: 8 KB
 constexpr int EPI_STAGE_BYTES = NUM_EPI_WARPS * EPI_WARP_STAGE_BYTES;
 
 template <int CTAS>
 struct Cfg {
-  static constexpr int STAGES = CTAS == 1 ? 4 : 6;
+  static constexpr int STAGES = CTAS == 1 ? 3 : 5;
   static constexpr int TILE_M = BM * CTAS;  // rows per tile of the CTA group
   static constexpr int B_ROWS = BN / CTAS;  // rows of the B tile this CTA stages
   static constexpr int A_STAGE_BYTES = BM * BK * 2;
@@ -141,11 +142,6 @@ __device__ __forceinline__ float gelu_tanh_approx(float x) {
   return fmaf(h, t, h);
 }
 
-__device__ __forceinline__ void ld_global_v8(const void* p, uint4& a, uint4& b) {
-  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
-               : "l"(p));
-}
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&v)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
                "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
@@ -160,6 +156,9 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all of this thread's earlier bulk stores have finished READING shared memory
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&v)[4]) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -203,7 +202,7 @@ struct ResidualRegs {
 template <typename OutT, bool GELU>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const float* bias_s, const EpilogueArgs<OutT>& e,
                                                const uint4* res_regs, int64_t row, int col0, int64_t N, int mode, uint32_t stage,
-                                               int half, int lane, bool row_ok, float& best_val, int& best_idx) {
+                                               int half, int lane, bool row_ok, bool res_staged, float& best_val, int& best_idx) {
   float f[32];
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
@@ -220,7 +219,22 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
   const bool full = col0 + 32 <= N;
   if constexpr (sizeof(OutT) == 2) {
     if (stage != 0 || (mode != STORE_SCALAR && full)) {
-      if (res_regs) {
+      if (res_staged) {
+        // residual tile already sits in this thread's slots of the staging box (zero outside the matrix)
+        const uint32_t rowaddr = stage + (uint32_t)lane * 128u;
+        const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t rw[4];
+          ld_shared_v4(rowaddr + ((((uint32_t)(half * 4 + g)) ^ sw) << 4), rw);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 r = unpack2<OutT>(rw[j]);
+            f[g * 8 + 2 * j] += r.x;
+            f[g * 8 + 2 * j + 1] += r.y;
+          }
+        }
+      } else if (res_regs) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const uint32_t* rw = reinterpret_cast<const uint32_t*>(&res_regs[g]);
@@ -306,7 +320,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
 template <typename OutT, bool GELU, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_out, EpilogueArgs<OutT> epi,
+               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res, EpilogueArgs<OutT> epi,
                int64_t M, int64_t N, int64_t K, uint32_t idesc, int* status_word) {
   using C = Cfg<CTAS>;
   constexpr int STAGES = C::STAGES;
@@ -328,9 +342,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t bar_acc_full = bar_empty + 8 * STAGES;
   const uint32_t bar_acc_empty = bar_acc_full + 16;
   const uint32_t bar_bias = bar_acc_empty + 16;
-  static_assert(8 * (2 * STAGES + 6) + 16 <= CTRL_BYTES, "control block too small");
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * STAGES + 6));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * (2 * STAGES + 6) + 8);
+  const uint32_t bar_res = bar_bias + 16;  // [NUM_EPI_WARPS]: residual boxes of a warp have landed
+  constexpr int NUM_BARS = 2 * STAGES + 6 + NUM_EPI_WARPS;
+  static_assert(8 * NUM_BARS + 16 <= CTRL_BYTES, "control block too small");
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * NUM_BARS + 8);
   float* bias_smem = reinterpret_cast<float*>(ctrl + CTRL_BYTES);  // [2][BN]
 
   const int warp = threadIdx.x >> 5;
@@ -354,6 +370,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(bar_acc_empty + 8 * a, NUM_EPI_WARPS * CTAS);  // the leader's barrier collects both CTAs' epilogue warps
       mbar_init(bar_bias + 8 * a, NUM_EPI_WARPS);
     }
+    for (int w = 0; w < NUM_EPI_WARPS; ++w) mbar_init(bar_res + 8 * w, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -462,33 +479,43 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (((out_al | res_al) & 15) == 0) mode = (esz == 2 && (out_al & 31) == 0) ? STORE_32B : STORE_16B;
     const uint32_t acc_empty_base = CTAS == 2 ? mapa_shared(bar_acc_empty, 0) : bar_acc_empty;
     const bool use_tma = esz == 2 && epi.tma_store != 0;
+    const bool res_tma = use_tma && epi.residual != nullptr;  // (the host only sets tma_store when the residual can be mapped too)
     const uint32_t stage_addr = use_tma ? smem_epi + (uint32_t)(warp - 2) * EPI_WARP_STAGE_BYTES : 0u;
+    const uint32_t my_res_bar = bar_res + 8 * (uint32_t)(warp - 2);
+    uint32_t res_phase = 0;
     for (int64_t t = group_id; t < num_tiles; t += num_groups) {
       const TileCoord tc = tile_coord<C::GROUP_M>(t, m_tiles, n_tiles);
       const int64_t row = (int64_t)tc.m * C::TILE_M + (int64_t)cta_rank * BM + quarter * 32 + lane;
       const int col_base = tc.n * BN + col_half * EPI_COLS;
+      const int row_warp = (int)(tc.m * C::TILE_M + (int)cta_rank * BM + quarter * 32);  // first row of this warp's 32
       const bool row_ok = row < M;
-      // Prefetch what does not depend on the accumulator: bias -> shared memory, residual -> registers.
+      // Prefetch what does not depend on the accumulator: bias -> shared memory, residual -> staging boxes (TMA)
+      // or registers.
+      if (use_tma) {
+        // both staging boxes are about to be overwritten: the previous tile's TMA stores must be done reading them
+        if (lane == 0) {
+          tma_store_wait_read();
+          if (res_tma) {
+            mbar_arrive_expect_tx(my_res_bar, EPI_WARP_STAGE_BYTES);
+#pragma unroll
+            for (int b = 0; b < EPI_COLS / EPI_BOX_COLS; ++b)
+              tma_load_2d(stage_addr + b * EPI_BOX_BYTES, &map_res, my_res_bar, col_base + b * EPI_BOX_COLS, row_warp);
+          }
+        }
+        __syncwarp();
+      }
       float* bias_s = bias_smem + acc * BN;
       for (int i = epi_tid; i < BN; i += 32 * NUM_EPI_WARPS) {
         const int c = tc.n * BN + i;
         bias_s[i] = (epi.bias && c < N) ? to_float(epi.bias[c]) : 0.f;
       }
       ResidualRegs res;
-      const bool res_in_regs = esz == 2 && epi.residual && mode != STORE_SCALAR && row_ok;
+      const bool res_in_regs = !use_tma && esz == 2 && epi.residual && mode != STORE_SCALAR && row_ok;
       if (res_in_regs) {
         const OutT* rrow = epi.residual + row * epi.ld_res + col_base;
-        if ((res_al & 31) == 0) {
-          // 32-byte loads: every request is a whole sector
 #pragma unroll
-          for (int i = 0; i < EPI_COLS / 8; i += 2) {
-            if (col_base + (i / 4) * 32 + 32 <= N) ld_global_v8(rrow + i * 8, res.v[i], res.v[i + 1]);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < EPI_COLS / 8; ++i) {
-            if (col_base + (i / 4) * 32 + 32 <= N) res.v[i] = *reinterpret_cast<const uint4*>(rrow + i * 8);
-          }
+        for (int i = 0; i < EPI_COLS / 8; ++i) {
+          if (col_base + (i / 4) * 32 + 32 <= N) res.v[i] = *reinterpret_cast<const uint4*>(rrow + i * 8);
         }
       }
       // bias visible to all epilogue warps (an mbarrier, not bar.sync: its wait is bounded like every other)
@@ -496,9 +523,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (lane == 0) mbar_arrive(bar_bias + 8 * acc);
       if (!mbar_wait(bar_bias + 8 * acc, acc_phase, abort_flag, status_word, 5)) break;
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, status_word, 4)) break;
+      if (res_tma) {
+        if (!mbar_wait(my_res_bar, res_phase, abort_flag, status_word, 6)) break;
+        res_phase ^= 1u;
+      }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_half * EPI_COLS);
-      const int row_warp = (int)(tc.m * C::TILE_M + (int)cta_rank * BM + quarter * 32);  // first row of this warp's 32
       float best_val = -INFINITY;
       int best_idx = 0;
 #pragma unroll
@@ -516,26 +546,22 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         const int col0 = col_base + c * 32;
         if (use_tma) {
-          if ((c & 1) == 0) {
-            // the staging tile is about to be overwritten: the previous TMA store must be done reading it
-            if (lane == 0) tma_store_wait_read();
-            __syncwarp();
-          }
+          const uint32_t box = stage_addr + (uint32_t)(c >> 1) * EPI_BOX_BYTES;
           if (col0 < N)
-            epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode,
-                                       stage_addr, c & 1, lane, row_ok, best_val, best_idx);
+            epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, nullptr, row, col0, N, mode, box, c & 1, lane, row_ok,
+                                       res_tma, best_val, best_idx);
           if ((c & 1) == 1) {
             fence_proxy_async_smem();
             __syncwarp();
             const int box_col = col_base + (c >> 1) * EPI_BOX_COLS;
             if (lane == 0 && box_col < N && row_warp < M) {
-              tma_store_2d(&map_out, stage_addr, box_col, row_warp);
+              tma_store_2d(&map_out, box, box_col, row_warp);
               tma_store_commit();
             }
           }
         } else if (row_ok && col0 < N) {
           epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode, 0u,
-                                     0, lane, row_ok, best_val, best_idx);
+                                     0, lane, row_ok, false, best_val, best_idx);
         }
       }
       if (epi.amax_val && row_ok) {
@@ -610,7 +636,7 @@ static int max_pairs() {
   return n;
 }
 
-// Map over the 16-bit output [M, N] (pitch ld_out) for tile stores of 64 columns x 32 rows.
+// Map over a 16-bit [M, N] matrix (pitch ld) for tile stores/loads of 64 columns x 32 rows (output, residual).
 static int make_out_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N, int64_t ld_out, int io_dtype) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return B200_ERR_CUDA;
@@ -624,7 +650,7 @@ static int make_out_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N, int64
 }
 
 template <typename OutT, bool GELU, int CTAS>
-static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const EpilogueArgs<OutT>& epi, int64_t M, int64_t N, int64_t K,
+static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mr, const EpilogueArgs<OutT>& epi, int64_t M, int64_t N, int64_t K,
                           int op_dtype, int64_t groups, int* status_word, cudaStream_t stream) {
   using C = Cfg<CTAS>;
   static bool attr_set = false;
@@ -644,7 +670,7 @@ static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CU
   attr.val.clusterDim.x = CTAS, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tn_kernel<OutT, GELU, CTAS>, ma, mb, mo, epi, M, N, K, idesc, status_word);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tn_kernel<OutT, GELU, CTAS>, ma, mb, mo, mr, epi, M, N, K, idesc, status_word);
   note_launches(1);
   return status_from_cuda(e);
 }
@@ -654,10 +680,14 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
                         int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, const ArgmaxPartials& am, int* status_word,
                         cudaStream_t stream) {
   EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.ld};
-  CUtensorMap mo;
+  CUtensorMap mo, mr;
   memset(&mo, 0, sizeof(mo));
+  memset(&mr, 0, sizeof(mr));
+  // TMA epilogue: 16-bit output (and residual, if any) with 16-byte aligned base and pitch
   if (sizeof(OutT) == 2 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_out % 8 == 0 &&
-      make_out_map(&mo, out, M, N, ld_out, DType<OutT>::code) == B200_OK)
+      (!residual || ((reinterpret_cast<uintptr_t>(residual) & 15) == 0 && ld_res % 8 == 0)) &&
+      make_out_map(&mo, out, M, N, ld_out, DType<OutT>::code) == B200_OK &&
+      (!residual || make_out_map(&mr, const_cast<void*>(residual), M, N, ld_res, DType<OutT>::code) == B200_OK))
     epi.tma_store = 1;
   const int64_t n_tiles = (N + BN - 1) / BN;
   const int pairs = M > BM ? max_pairs<OutT, GELU>() : 0;
@@ -668,13 +698,13 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
     st = make_map(&mb, b, N, K, ldb, Cfg<2>::B_ROWS, op_dtype);
     if (st != B200_OK) return st;
     const int64_t tiles = ((M + Cfg<2>::TILE_M - 1) / Cfg<2>::TILE_M) * n_tiles;
-    return launch_variant<OutT, GELU, 2>(ma, mb, mo, epi, M, N, K, op_dtype, tiles < pairs ? tiles : pairs, status_word, stream);
+    return launch_variant<OutT, GELU, 2>(ma, mb, mo, mr, epi, M, N, K, op_dtype, tiles < pairs ? tiles : pairs, status_word, stream);
   }
   st = make_map(&mb, b, N, K, ldb, Cfg<1>::B_ROWS, op_dtype);
   if (st != B200_OK) return st;
   const int64_t tiles = ((M + BM - 1) / BM) * n_tiles;
   const int64_t sms = sm_count();
-  return launch_variant<OutT, GELU, 1>(ma, mb, mo, epi, M, N, K, op_dtype, tiles < sms ? tiles : sms, status_word, stream);
+  return launch_variant<OutT, GELU, 1>(ma, mb, mo, mr, epi, M, N, K, op_dtype, tiles < sms ? tiles : sms, status_word, stream);
 }
 
 }  // namespace gemm
