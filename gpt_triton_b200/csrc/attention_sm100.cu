@@ -1,4 +1,7 @@
-// Causal flash attention on the 5th-generation tensor cores, head size 64, 16-bit storage.
+// Causal flash attention on the 5th-generation tensor cores, head size 64, fp16 or bf16 storage.
+// bf16 Q and K feed S = Q K^T as they are (exact products).  P is fp16 for both storage types, as in the
+// reference, and both operands of one MMA must have the same format, so a bf16 V tile is converted to
+// fp16 in place (exact in fp16's normal range) by the softmax warps before P V.
 //
 // Work item = 128 query rows of one (batch, head).  Persistent CTAs (two per SM) walk the items,
 // longest first.  Per CTA:
@@ -83,6 +86,9 @@ __device__ __forceinline__ float ex2f(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&v)[4]) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr) : "memory");
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -108,6 +114,7 @@ template <typename T>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, Params p, uint32_t idesc_s, uint32_t idesc_pv) {
+  constexpr bool IS_FP16 = DType<T>::code == B200_F16;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -340,7 +347,23 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             st_shared_v4(p_row + ((chunk ^ sw) << 4), w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
           }
         }
-        // S[sb] is free; P is complete
+        if constexpr (sizeof(T) == 2 && !IS_FP16) {
+          // bf16 storage: V_j -> fp16 in place, 64 bytes per softmax thread (the swizzle is address-agnostic)
+          const uint32_t vaddr = smem_kv + (it_count % KV_STAGES) * KV_STAGE_BYTES + KV_TILE_BYTES + (uint32_t)(threadIdx.x - 64) * 64u;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t w4[4];
+            ld_shared_v4(vaddr + g * 16, w4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f2 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w4[i]));
+              const __half2 h2 = __floats2half2_rn(f2.x, f2.y);
+              w4[i] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            st_shared_v4(vaddr + g * 16, w4[0], w4[1], w4[2], w4[3]);
+          }
+        }
+        // S[sb] is free; P (and, for bf16, the converted V) is complete
         tc_fence_before();
         fence_proxy_async_smem();
         __syncwarp();
@@ -465,7 +488,7 @@ int launch_attention_sm100(const void* q, const void* k, const void* v, void* ou
                            const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale, int in_dtype,
                            int out_dtype, int* status_word, cudaStream_t stream) {
   using namespace attn100;
-  if (Dh != D || in_dtype != out_dtype || in_dtype != B200_F16) return B200_ERR_UNSUPPORTED;
+  if (Dh != D || in_dtype != out_dtype || (in_dtype != B200_F16 && in_dtype != B200_BF16)) return B200_ERR_UNSUPPORTED;
   if (!view_ok(q, qs, B, NH) || !view_ok(k, ks, B, NH) || !view_ok(v, vs, B, NH) || !view_ok(out, os, B, NH)) return B200_ERR_UNSUPPORTED;
   if (B * NH > 0x7fffffffLL || L > 0x7fffff00LL || B > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
   CUtensorMap mq, mk, mv;
@@ -476,7 +499,9 @@ int launch_attention_sm100(const void* q, const void* k, const void* v, void* ou
   if (st != B200_OK) return B200_ERR_UNSUPPORTED;  // e.g. strides the tensor map cannot express
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attention_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return B200_ERR_CUDA;
+    if (cudaFuncSetAttribute(attention_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return B200_ERR_CUDA;
     attr_set = true;
   }
   p.out = out;
@@ -488,7 +513,11 @@ int launch_attention_sm100(const void* q, const void* k, const void* v, void* ou
   const int64_t n_items = ((L + BLOCK_M - 1) / BLOCK_M) * B * NH;
   int64_t grid = (int64_t)sm_count() * 2;
   if (grid > n_items) grid = n_items;
-  attention_sm100_kernel<__half><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p, idesc(0, 0, 0), idesc(0, 0, 1));
+  // S = Q K^T in the storage format; P V always fp16 x fp16 (see the top of this file)
+  if (in_dtype == B200_BF16)
+    attention_sm100_kernel<__nv_bfloat16><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p, idesc(1, 1, 0), idesc(0, 0, 1));
+  else
+    attention_sm100_kernel<__half><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p, idesc(0, 0, 0), idesc(0, 0, 1));
   note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }

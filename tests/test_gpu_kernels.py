@@ -284,15 +284,16 @@ def test_attention_vs_oracle(B, N, L, H, dtype, dist):
 
 @pytest.mark.parametrize("B,N,L", [(2, 3, 300), (1, 2, 64), (1, 1, 129), (3, 2, 1000), (1, 12, 1), (2, 2, 128)])
 @pytest.mark.parametrize("layout", ["contiguous", "fused_qkv"])
-def test_attention_tensor_core_path_fp16(B, N, L, layout):
-    """Head size 64, fp16: the tcgen05/TMA kernel, from contiguous [B, N, L, 64] tensors and from
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_attention_tensor_core_path_16bit(B, N, L, layout, dtype):
+    """Head size 64, fp16/bf16: the tcgen05/TMA kernel, from contiguous [B, N, L, 64] tensors and from
     strided views of a fused [B, L, 3*N*64] projection, writing contiguous and merged-head output."""
     g = torch.Generator().manual_seed(B * 100 + L)
     if layout == "contiguous":
-        q, k, v = (torch.randn((B, N, L, 64), generator=g).half() for _ in range(3))
+        q, k, v = (torch.randn((B, N, L, 64), generator=g).to(dtype) for _ in range(3))
         qc, kc, vc = cu(q), cu(k), cu(v)
     else:
-        qkv = torch.randn((B, L, 3 * N * 64), generator=g).half()
+        qkv = torch.randn((B, L, 3 * N * 64), generator=g).to(dtype)
         q, k, v = (t.reshape(B, L, N, 64).transpose(1, 2) for t in qkv.split(N * 64, dim=2))
         qc, kc, vc = (t.reshape(B, L, N, 64).transpose(1, 2) for t in cu(qkv).split(N * 64, dim=2))
     ref = orc.flash_attention_v1(q.contiguous(), k.contiguous(), v.contiguous())
