@@ -213,27 +213,44 @@ def run_gpu_arm(args, rank, world, local_rank):
     e2e_value = world * tokens_per_step / (e2e_ms * 1e-3)
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA events around every GEMM launch
-    # of further forward passes, on the stream the kernels are launched on.
+    # of further forward passes, on the stream the kernels are launched on.  The other operators are
+    # bracketed the same way to give the per-step breakdown.
     records = []
-    orig_ffn = K.fused_ffn
+    other = {"attention": [], "layernorm": [], "embedding": []}
+    orig = {"fused_ffn": K.fused_ffn, "flash_attention_v1": K.flash_attention_v1, "fused_layer_norm": K.fused_layer_norm,
+            "fused_embeddings": K.fused_embeddings}
 
     def timed_ffn(x, weight, *a, **kw):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        z = orig_ffn(x, weight, *a, **kw)
+        z = orig["fused_ffn"](x, weight, *a, **kw)
         e.record()
         m = x.numel() // x.shape[-1]
         records.append((m, weight.N, weight.K, s, e))
         return z
 
+    def timed(kind, name):
+        def fn(*a, **kw):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            z = orig[name](*a, **kw)
+            e.record()
+            other[kind].append((s, e))
+            return z
+        return fn
+
     K.fused_ffn = timed_ffn
+    K.flash_attention_v1 = timed("attention", "flash_attention_v1")
+    K.fused_layer_norm = timed("layernorm", "fused_layer_norm")
+    K.fused_embeddings = timed("embedding", "fused_embeddings")
     probe_steps = min(3, args.steps)
     try:
         for _ in range(probe_steps):
             model.logits(ids_dev)
         torch.cuda.synchronize()
     finally:
-        K.fused_ffn = orig_ffn
+        for name, fn in orig.items():
+            setattr(K, name, fn)
     gemm_ms = sum(s.elapsed_time(e) for *_, s, e in records)
     gemm_flop = sum(2.0 * m * n * k for m, n, k, _, _ in records)
     achieved_tflops = gemm_flop / (gemm_ms * 1e-3) / 1e12
@@ -245,6 +262,11 @@ def run_gpu_arm(args, rank, world, local_rank):
         d[1] += 1
     detail = {f"{m}x{n}x{k}": {"launches_per_step": c // probe_steps, "avg_ms": t / c, "tflops": 2.0 * m * n * k / (t / c * 1e-3) / 1e12}
               for (m, n, k), (t, c) in by_shape.items()}
+
+    breakdown = {"gemm": gemm_ms / probe_steps}
+    for kind, evs in other.items():
+        breakdown[kind] = sum(s.elapsed_time(e) for s, e in evs) / probe_steps
+    breakdown["unattributed"] = ms_per_step - sum(breakdown.values())
 
     flops = executed_fwd_flops(gcfg, BATCH, SEQ)
     per_gpu_flops_s = flops / (ms_per_step * 1e-3)
@@ -264,6 +286,7 @@ def run_gpu_arm(args, rank, world, local_rank):
                        "batch_per_gpu": BATCH, "seq_len": SEQ, "global_batch": BATCH * world, "parallelism": f"batch-sharded replicas x{world}",
                        "l2": "no flush: each step streams > 20 GB of activations and logits, far beyond the 126 MB L2",
                        "flop_per_step_per_gpu": flops},
+            "breakdown_ms_per_step": breakdown,
             "mfu": {"of_spec_2250": per_gpu_flops_s / 2250e12, f"of_{peak_kind}_sustained": per_gpu_flops_s / (peak_tflops * 1e12)},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ids_host.numel() * 8,
                     "d2h_bytes_per_step": out_host.numel() * 8,

@@ -81,6 +81,11 @@ __device__ __forceinline__ Item decode_item(int64_t idx, int bh_total, int n_qt,
   return it;
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -286,10 +291,10 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc_fence_after();
         const uint32_t s_addr = tmem_s + lane_addr + sb * BLOCK_N;
         const int k0 = j * BLOCK_N;
-        const bool need_mask = k0 + BLOCK_N - 1 > it.q0;  // some key of this block lies above some row's diagonal
         // a 32-key chunk whose first key lies above this warp's last row is masked for the whole warp
         const int live_chunks = (!warp_live || k0 > warp_row0 + 31) ? 0 : (k0 + 32 > warp_row0 + 31 ? 1 : 2);
-        // pass 1: block maximum of the raw scores (the scale is positive, so it commutes with max)
+        // pass 1: block maximum of the raw scores (the scale is positive, so it commutes with max).  A 32-key
+        // chunk needs per-element masking only if the diagonal crosses it for some row of this warp.
         float bm = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -297,11 +302,13 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           uint32_t v[32];
           tmem_ld_32x32(s_addr + c * 32, v);
           tmem_ld_wait();
+          if (k0 + c * 32 + 31 > warp_row0) {
+            const int lim = row - k0 - c * 32;  // keys i <= lim are visible to this row
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(v[i]);
-            if (need_mask && k0 + c * 32 + i > row) x = -INFINITY;
-            bm = fmaxf(bm, x);
+            for (int i = 0; i < 32; ++i) bm = fmaxf(bm, i > lim ? -INFINITY : __uint_as_float(v[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) bm = fmax3(bm, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
           }
         }
         const float m_new = fmaxf(m_run, bm * p.scale_log2e);  // running maximum, in log2 units
@@ -328,18 +335,27 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tmem_ld_32x32(s_addr + c * 32, v);
           tmem_ld_wait();
           uint32_t w[16];
+          if (k0 + c * 32 + 31 > warp_row0) {
+            const int lim = row - k0 - c * 32;
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0 = fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new);
-            float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m_new);
-            if (need_mask) {
-              if (k0 + c * 32 + i > row) x0 = -INFINITY;
-              if (k0 + c * 32 + i + 1 > row) x1 = -INFINITY;
+            for (int i = 0; i < 32; i += 2) {
+              const float x0 = fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new);
+              const float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m_new);
+              const float p0 = i > lim ? 0.f : ex2f(x0);
+              const float p1 = i + 1 > lim ? 0.f : ex2f(x1);
+              psum += p0 + p1;
+              __half2 h = __floats2half2_rn(p0, p1);
+              w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
             }
-            const float p0 = ex2f(x0), p1 = ex2f(x1);
-            psum += p0 + p1;
-            __half2 h = __floats2half2_rn(p0, p1);
-            w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = ex2f(fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new));
+              const float p1 = ex2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m_new));
+              psum += p0 + p1;
+              __half2 h = __floats2half2_rn(p0, p1);
+              w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+            }
           }
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
