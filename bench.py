@@ -28,6 +28,11 @@ if ROOT not in sys.path:
 
 GPT2_SMALL = dict(vocab_size=50257, block_size=1024, n_layer=12, n_head=12, n_embd=768, dropout=0.1)
 BATCH, SEQ = 512, 300
+# the larger, attention-heavier configurations (not the headline; `--model` times them on one GPU)
+OTHER_MODELS = {
+    "355m": (dict(vocab_size=50257, block_size=1024, n_layer=24, n_head=16, n_embd=1024, dropout=0.1), 256, 1024, torch.bfloat16),
+    "1.5b": (dict(vocab_size=50257, block_size=1024, n_layer=48, n_head=25, n_embd=1600, dropout=0.1), 128, 1024, torch.bfloat16),
+}
 CPU_SAMPLE_BATCH = 16  # sequences per CPU-baseline step (the full batch would take minutes per step)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -367,6 +372,42 @@ def run_sweep(args):
             del qkv, q, k, v
 
 
+def run_other_model(args):
+    """Forward + lm_head throughput of GPT-2 medium / XL (bf16, seq 1024) on one GPU: weights N(0, 0.02) drawn on
+    the device, uniform ids.  Extra figure for the record, not the headline metric."""
+    from gpt_triton_b200.gpt import FusedGPT, GPTConfig, executed_fwd_flops
+
+    kw, batch, seq, dtype = OTHER_MODELS[args.model]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = FusedGPT(GPTConfig(**kw))
+    with torch.no_grad():
+        for name, prm in model.named_parameters():
+            if prm.dim() == 2:
+                prm.normal_(0.0, 0.02)
+            elif name.endswith("layer_norm_weight"):
+                prm.fill_(1.0)
+            else:
+                prm.zero_()
+    model = model.to(dtype).eval()
+    ids = torch.randint(0, kw["vocab_size"], (batch, seq), device=dev)
+    for _ in range(args.warmup):
+        model.logits(ids)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.steps):
+        model.logits(ids)
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / args.steps
+    flops = executed_fwd_flops(GPTConfig(**kw), batch, seq)
+    print(json.dumps({"model": args.model, "batch": batch, "seq_len": seq, "dtype": str(dtype).replace("torch.", ""), "ms_per_step": ms,
+                      "tokens_per_s": batch * seq / (ms * 1e-3), "flop_per_step": flops, "mfu_of_spec_2250": flops / (ms * 1e-3) / 2250e12}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,9 +419,13 @@ def main():
                     help="time single kernels at the kernel-sweep shapes instead of the forward")
     ap.add_argument("--rows", type=int, default=0, help="--sweep: rows (tokens) instead of 153600")
     ap.add_argument("--batch", type=int, default=0, help="--sweep attention: batch instead of 512")
+    ap.add_argument("--model", default=None, choices=sorted(OTHER_MODELS), help="time a larger GPT-2 instead of the 124M headline")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)
+        return
+    if args.model:
+        run_other_model(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
 

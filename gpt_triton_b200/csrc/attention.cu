@@ -9,6 +9,8 @@
 // fp16 relative to the running maximum of each 64-key block and the running maximum and
 // denominator are fp32 -- the arithmetic of the reference's flash_attention_v1 kernel.  Key
 // blocks that the causal mask removes entirely are skipped (they contribute exact zeros).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -263,11 +265,13 @@ template <int D, typename TIn, typename TOut>
 static int launch_typed(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L,
                         Strides sq, Strides sk, Strides sv, Strides so, float scale, cudaStream_t stream) {
   constexpr size_t smem = smem_bytes<D>();
-  static bool attr_set = false;
-  if (!attr_set && smem > 48 * 1024) {
+  static std::atomic<bool> attr_set[kMaxDevices];  // kernel attributes are per device
+  const int slot = device_slot();
+  if (slot < 0) return B200_ERR_CUDA;
+  if (smem > 48 * 1024 && !attr_set[slot].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(attention_kernel<D, TIn, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return B200_ERR_CUDA;
-    attr_set = true;
+    attr_set[slot].store(true, std::memory_order_release);
   }
   auto ok_in = [](const void* p, const Strides& s) {
     const int64_t m = sizeof(TIn) == 4 ? 4 : 8;

@@ -17,6 +17,8 @@
 // The softmax runs over 64-key blocks with P rounded relative to the running maximum of each
 // block, which is the arithmetic of the reference's flash_attention_v1 kernel (kernels.py:417-474
 // of the reference); blocks above the diagonal are skipped.  Every mbarrier wait is bounded.
+#include <atomic>
+
 #include "sm100_primitives.cuh"
 
 namespace b200 {
@@ -513,12 +515,14 @@ int launch_attention_sm100(const void* q, const void* k, const void* v, void* ou
   if (st == B200_OK) st = make_map(&mk, k, B, NH, L, ks, BLOCK_N, in_dtype, &p.k_head_inner);
   if (st == B200_OK) st = make_map(&mv, v, B, NH, L, vs, BLOCK_N, in_dtype, &p.v_head_inner);
   if (st != B200_OK) return B200_ERR_UNSUPPORTED;  // e.g. strides the tensor map cannot express
-  static bool attr_set = false;
-  if (!attr_set) {
+  static std::atomic<bool> attr_set[kMaxDevices];  // kernel attributes are per device
+  const int slot = device_slot();
+  if (slot < 0) return B200_ERR_CUDA;
+  if (!attr_set[slot].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(attention_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
         cudaFuncSetAttribute(attention_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return B200_ERR_CUDA;
-    attr_set = true;
+    attr_set[slot].store(true, std::memory_order_release);
   }
   p.out = out;
   p.so_b = os[0], p.so_h = os[1], p.so_l = os[2];

@@ -124,6 +124,9 @@ __device__ __forceinline__ float gelu_new(float x) {
 inline int status_from_cuda(cudaError_t e) { return e == cudaSuccess ? B200_OK : B200_ERR_CUDA; }
 
 int sm_count();  // cached multiprocessor count of the current device
+// Index of the current device for per-device caches (kernel attributes, occupancy figures); -1 if it cannot be had.
+constexpr int kMaxDevices = 64;
+int device_slot();
 void note_launches(int n);  // adds to the library-wide count of kernels launched
 uint64_t launches_so_far();
 

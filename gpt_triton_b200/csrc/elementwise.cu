@@ -11,15 +11,22 @@ static std::atomic<uint64_t> g_launches{0};
 void note_launches(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 uint64_t launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
 
-static int g_sm_count = 0;
+int device_slot() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
+static std::atomic<int> g_sm_count[kMaxDevices];
 int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
-    g_sm_count = n;
+  const int slot = device_slot();
+  if (slot < 0) return 148;
+  int n = g_sm_count[slot].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, slot) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count[slot].store(n, std::memory_order_relaxed);
   }
-  return g_sm_count;
+  return n;
 }
 
 constexpr int kWarpsPerBlock = 8;

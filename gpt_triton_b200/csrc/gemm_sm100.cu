@@ -23,6 +23,8 @@
 // CTA-wide abort flag, reports through status_word and the kernel drains and exits.
 #include <string.h>
 
+#include <atomic>
+
 #include "sm100_primitives.cuh"
 
 namespace b200 {
@@ -612,11 +614,15 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t col
 // Largest number of 2-CTA clusters of this kernel that can be resident at once (cached per instantiation).
 template <typename OutT, bool GELU>
 static int max_pairs() {
-  static int cached = -1;
-  if (cached >= 0) return cached;
+  static std::atomic<int> cache[kMaxDevices];  // per device; stored as value + 1 so that 0 means "not asked yet"
+  const int slot = device_slot();
+  if (slot < 0) return 0;
+  const int seen = cache[slot].load(std::memory_order_acquire);
+  if (seen > 0) return seen - 1;
   if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES) != cudaSuccess) {
     cudaGetLastError();
-    return cached = 0;
+    cache[slot].store(1, std::memory_order_release);
+    return 0;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)sm_count() / 2 * 2);
@@ -632,7 +638,7 @@ static int max_pairs() {
     cudaGetLastError();
     n = 0;
   }
-  cached = n;
+  cache[slot].store(n + 1, std::memory_order_release);
   return n;
 }
 
@@ -653,11 +659,13 @@ template <typename OutT, bool GELU, int CTAS>
 static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mr, const EpilogueArgs<OutT>& epi, int64_t M, int64_t N, int64_t K,
                           int op_dtype, int64_t groups, int* status_word, cudaStream_t stream) {
   using C = Cfg<CTAS>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static std::atomic<bool> attr_set[kMaxDevices];  // kernel attributes are per device
+  const int slot = device_slot();
+  if (slot < 0) return B200_ERR_CUDA;
+  if (!attr_set[slot].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
       return B200_ERR_CUDA;
-    attr_set = true;
+    attr_set[slot].store(true, std::memory_order_release);
   }
   const uint32_t idesc = make_idesc(op_dtype == B200_BF16 ? 1 : 0, BM * CTAS);
   cudaLaunchConfig_t cfg = {};

@@ -123,6 +123,28 @@ def test_gpt2_small_fp16_vs_oracle_and_batch_independence():
     assert torch.equal(next_ids[sel.to(DEV)].cpu(), first)
 
 
+@pytest.mark.parametrize("name,kw,B,L", [
+    ("gpt2-medium", dict(vocab_size=50257, block_size=1024, n_layer=24, n_head=16, n_embd=1024, dropout=0.1), 2, 160),
+    ("gpt2-xl-8-layers", dict(vocab_size=50257, block_size=1024, n_layer=8, n_head=25, n_embd=1600, dropout=0.1), 2, 130),
+])
+def test_bf16_medium_and_xl_shapes_vs_oracle(name, kw, B, L):
+    """GPT-2 medium (355M, full depth) and GPT-2 XL widths (h=1600, 25 heads; 8 of the 48 layers to keep
+    the CPU oracle quick), bf16 storage, N(0, 0.02) weights, uniform ids.  bf16 has 8 significant bits:
+    one ulp is 1.6e-2 for |x| in [2, 4) and 3.1e-2 in [4, 8), so the bound is a few ulps: logits
+    within 0.1, argmax equal wherever the oracle's top-2 margin exceeds 2 ulps (6.25e-2)."""
+    model, cfg, sd = build_model(kw, torch.bfloat16)
+    ids = torch.randint(0, 50257, (B, L), generator=torch.Generator().manual_seed(0))
+    hidden = model(ids.to(DEV))
+    logits, next_ids = model.lm_head(hidden, return_argmax=True)
+    ref_hidden = orc.gpt_forward(sd, cfg, ids)
+    ref_logits = orc.lm_head(sd, ref_hidden)
+    assert (hidden.cpu().float() - ref_hidden.float()).abs().max().item() < 0.2
+    assert (logits.cpu().float() - ref_logits.float()).abs().max().item() < 0.1
+    assert (logits.cpu().float() - ref_logits.float()).abs().mean().item() < 0.015
+    _argmax_agrees_where_clear(logits.cpu(), ref_logits, 6.25e-2)
+    assert torch.equal(logits.gather(2, next_ids[..., None])[..., 0], logits.max(dim=-1).values)
+
+
 def test_training_mode_rejected():
     model, _, _ = build_model(TINY, torch.float32)
     model.train()
