@@ -348,3 +348,38 @@ def test_attention_asserts():
     q = torch.rand(1, 2, 8, 32, device=DEV)
     with pytest.raises(NotImplementedError):
         k.flash_attention_v1(q, q, q, dropout_prob=0.1)
+
+
+# ----------------------------------------------------------------------------- edge cases
+def test_empty_inputs_are_no_ops():
+    k = K()
+    wte, wpe = torch.rand(10, 64, device=DEV), torch.rand(8, 64, device=DEV)
+    assert k.fused_embeddings(torch.zeros((0, 5), dtype=torch.long, device=DEV), wte, wpe).shape == (0, 5, 64)
+    assert k.fused_layer_norm(torch.zeros((0, 64), device=DEV), torch.ones(64, device=DEV), torch.zeros(64, device=DEV)).shape == (0, 64)
+    assert k.fused_ffn(torch.zeros((0, 64), device=DEV), torch.rand(64, 32, device=DEV)).shape == (0, 32)
+    q = torch.zeros((0, 2, 7, 64), device=DEV, dtype=torch.float16)
+    assert k.flash_attention_v1(q, q, q).shape == (0, 2, 7, 64)
+    torch.cuda.synchronize()
+
+
+def test_single_token_and_single_row():
+    k = K()
+    g = torch.Generator().manual_seed(5)
+    for dtype in (torch.float32, torch.float16):
+        q, kk, v = (torch.randn((2, 3, 1, 64), generator=g).to(dtype) for _ in range(3))
+        z = k.flash_attention_v1(cu(q), cu(kk), cu(v))
+        assert_close(z, v.half().to(dtype), scale_big=False)  # one key: softmax is 1, output is the fp16-rounded v
+        assert_close(z, orc.flash_attention_v1(q, kk, v), scale_big=False)
+        x, w, b, _ = _ffn_inputs(1, 768, 768, dtype, seed=3)
+        assert_close(k.fused_ffn(cu(x), cu(w), bias=cu(b), add_gelu=True), orc.fused_ffn(x, w, b, None, True))
+
+
+def test_non_contiguous_inputs_are_rejected_like_the_reference():
+    k = K()
+    x = torch.rand(8, 16, device=DEV)
+    with pytest.raises(AssertionError):
+        k.fused_layer_norm(x.t(), torch.ones(8, device=DEV), torch.zeros(8, device=DEV))
+    with pytest.raises(AssertionError):
+        k.fused_embeddings(torch.zeros((4, 6), dtype=torch.long, device=DEV).t(), torch.rand(4, 8, device=DEV), torch.rand(8, 8, device=DEV))
+    with pytest.raises(AssertionError):
+        k.fused_ffn(x, torch.rand(8, 16, device=DEV).t())
