@@ -158,6 +158,8 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all of this thread's earlier bulk stores have finished READING shared memory
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... all but the most recent one
+__device__ __forceinline__ void tma_store_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&v)[4]) {
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
 }
@@ -493,11 +495,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool row_ok = row < M;
       // Prefetch what does not depend on the accumulator: bias -> shared memory, residual -> staging boxes (TMA)
       // or registers.
-      if (use_tma) {
-        // both staging boxes are about to be overwritten: the previous tile's TMA stores must be done reading them
+      if (res_tma) {
+        // both staging boxes are about to be overwritten by the residual: the previous tile's TMA stores must be done reading them
         if (lane == 0) {
           tma_store_wait_read();
-          if (res_tma) {
+          {
             mbar_arrive_expect_tx(my_res_bar, EPI_WARP_STAGE_BYTES);
 #pragma unroll
             for (int b = 0; b < EPI_COLS / EPI_BOX_COLS; ++b)
@@ -549,6 +551,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int col0 = col_base + c * 32;
         if (use_tma) {
           const uint32_t box = stage_addr + (uint32_t)(c >> 1) * EPI_BOX_BYTES;
+          if (!res_tma && (c & 1) == 0) {
+            // about to overwrite this box: its store of the previous tile is the second most recent bulk group
+            if (lane == 0) tma_store_wait_read_but_one();
+            __syncwarp();
+          }
           if (col0 < N)
             epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, nullptr, row, col0, N, mode, box, c & 1, lane, row_ok,
                                        res_tma, best_val, best_idx);
@@ -556,9 +563,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             fence_proxy_async_smem();
             __syncwarp();
             const int box_col = col_base + (c >> 1) * EPI_BOX_COLS;
-            if (lane == 0 && box_col < N && row_warp < M) {
-              tma_store_2d(&map_out, box, box_col, row_warp);
-              tma_store_commit();
+            if (lane == 0) {
+              if (box_col < N && row_warp < M) tma_store_2d(&map_out, box, box_col, row_warp);
+              tma_store_commit();  // always one bulk group per box and tile (possibly empty): the waits above count groups
             }
           }
         } else if (row_ok && col0 < N) {
