@@ -70,7 +70,7 @@ def ref_test_inputs(M, K, N):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of thevasudevgupta/gpt-triton")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     install_bool_shim()
