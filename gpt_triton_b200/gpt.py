@@ -190,6 +190,36 @@ class FusedGPT(_EvalOnly):
         return total
 
 
+class GraphedForward:
+    """One forward of a FusedGPT for a fixed (batch, seqlen), captured in a CUDA graph and replayed.
+
+    The 87 kernel launches of a 12-layer forward cost the host a few milliseconds; at small batches that is
+    more than the GPU needs (8 x 300 tokens: 2.9 ms eager, 1.4 ms replayed on a B200).  ``what`` selects the
+    captured method: "forward" (hidden state), "logits" or "logits_and_next_ids".  The results are static
+    buffers that every call overwrites; clone them to keep them."""
+
+    def __init__(self, model, example_ids, what="logits", warmup=3):
+        assert what in ("forward", "logits", "logits_and_next_ids")
+        self._fn = getattr(model, what)
+        self.static_ids = example_ids.clone()
+        # warm-up on a side stream: first calls set kernel attributes, pack weights and fill the allocator's pool
+        side = torch.cuda.Stream(device=example_ids.device)
+        side.wait_stream(torch.cuda.current_stream(example_ids.device))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(max(1, warmup)):
+                self._fn(self.static_ids)
+        torch.cuda.current_stream(example_ids.device).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.outputs = self._fn(self.static_ids)
+
+    def __call__(self, ids):
+        assert ids.shape == self.static_ids.shape, "a captured forward serves one (batch, seqlen) only"
+        self.static_ids.copy_(ids)
+        self.graph.replay()
+        return self.outputs
+
+
 def executed_fwd_flops(config, batch, seqlen, with_lm_head=True):
     """Tensor-core flop one forward really executes: the four projections of every layer,
     causal attention (QK^T and PV over the lower triangle) and optionally the tied lm_head."""

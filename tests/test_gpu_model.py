@@ -145,6 +145,24 @@ def test_bf16_medium_and_xl_shapes_vs_oracle(name, kw, B, L):
     assert torch.equal(logits.gather(2, next_ids[..., None])[..., 0], logits.max(dim=-1).values)
 
 
+def test_cuda_graph_replay_matches_eager():
+    """The whole forward + lm_head + fused argmax captured in a CUDA graph: replays give the eager bits, for the
+    captured ids and for new ones."""
+    from gpt_triton_b200.gpt import GraphedForward
+
+    model, _, _ = build_model(TINY, torch.float16, random_affine=True)
+    g = torch.Generator().manual_seed(3)
+    ids_a = torch.randint(0, 1024, (4, 96), generator=g).to(DEV)
+    ids_b = torch.randint(0, 1024, (4, 96), generator=g).to(DEV)
+    graphed = GraphedForward(model, ids_a, what="logits_and_next_ids")
+    for ids in (ids_a, ids_b, ids_a):
+        logits, nxt = graphed(ids)
+        ref_logits, ref_nxt = model.logits_and_next_ids(ids)
+        assert torch.equal(logits, ref_logits) and torch.equal(nxt, ref_nxt)
+    with pytest.raises(AssertionError):
+        graphed(ids_a[:2])
+
+
 def test_training_mode_rejected():
     model, _, _ = build_model(TINY, torch.float32)
     model.train()
