@@ -383,3 +383,44 @@ def test_non_contiguous_inputs_are_rejected_like_the_reference():
         k.fused_embeddings(torch.zeros((4, 6), dtype=torch.long, device=DEV).t(), torch.rand(4, 8, device=DEV), torch.rand(8, 8, device=DEV))
     with pytest.raises(AssertionError):
         k.fused_ffn(x, torch.rand(8, 16, device=DEV).t())
+
+
+# ----------------------------------------------------------------------------- seeded random shapes
+def test_ffn_random_shapes_all_epilogues():
+    """40 seeded random (M, N, K, dtype, epilogue) problems, ragged in every dimension, both kernel variants
+    (single CTA for M <= 128, CTA pair above), TMA and register epilogues (N or K not multiples of 8)."""
+    rng = torch.Generator().manual_seed(2024)
+    k = K()
+    for case in range(40):
+        M = int(torch.randint(1, 700, (1,), generator=rng))
+        N = int(torch.randint(1, 900, (1,), generator=rng))
+        K_ = int(torch.randint(1, 400, (1,), generator=rng))
+        if case % 3 == 0:
+            N, K_ = (N + 7) // 8 * 8, (K_ + 7) // 8 * 8  # aligned: operands in place, TMA epilogue
+        dtype = (torch.float16, torch.bfloat16, torch.float32)[case % 3 if case % 5 else 0]
+        gelu, use_b, use_r = bool(case & 1), bool(case & 2), bool(case & 4)
+        x, w, b, r = _ffn_inputs(M, N, K_, dtype, seed=1000 + case)
+        z = k.fused_ffn(cu(x), cu(w), bias=cu(b) if use_b else None, residual=cu(r) if use_r else None, add_gelu=gelu)
+        ref = orc.fused_ffn(x, w, b if use_b else None, r if use_r else None, gelu)
+        try:
+            assert_close(z, ref)
+        except AssertionError as e:
+            raise AssertionError(f"case {case}: M={M} N={N} K={K_} {dtype} gelu={gelu} bias={use_b} res={use_r}: {e}") from None
+
+
+def test_attention_random_shapes():
+    """24 seeded random (B, heads, L, head size, dtype) problems against the oracle."""
+    rng = torch.Generator().manual_seed(77)
+    k = K()
+    for case in range(24):
+        B = int(torch.randint(1, 4, (1,), generator=rng))
+        N = int(torch.randint(1, 5, (1,), generator=rng))
+        L = int(torch.randint(1, 520, (1,), generator=rng))
+        H = (64, 64, 32, 16, 128)[case % 5]
+        dtype = (torch.float16, torch.bfloat16, torch.float32)[case % 3]
+        q, kk, v = (torch.randn((B, N, L, H), generator=rng).to(dtype) for _ in range(3))
+        z = k.flash_attention_v1(cu(q), cu(kk), cu(v))
+        try:
+            assert_close(z, orc.flash_attention_v1(q, kk, v), scale_big=False, floor=ATTN_TOL)
+        except AssertionError as e:
+            raise AssertionError(f"case {case}: B={B} N={N} L={L} H={H} {dtype}: {e}") from None
