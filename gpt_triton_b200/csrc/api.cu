@@ -33,7 +33,7 @@ const char* b200_status_string(int status) {
 
 const char* b200_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
 
-int b200_abi_version(void) { return 1; }
+int b200_abi_version(void) { return 2; }
 
 uint64_t b200_launch_count(void) { return b200::launches_so_far(); }
 
@@ -74,10 +74,11 @@ size_t b200_gemm_argmax_workspace_bytes(int64_t M, int64_t N) { return b200::gem
 
 int b200_gemm_argmax(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                      int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
-                     int add_gelu, int64_t* argmax_out, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+                     int add_gelu, int64_t* argmax_out, float* lse_out, void* workspace, size_t workspace_bytes, int* status_word,
+                     void* stream) {
   if (!valid_dtype(io_dtype) || !argmax_out) return B200_ERR_BAD_ARGUMENT;
   return note(b200::launch_gemm_argmax(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, io_dtype, add_gelu,
-                                       argmax_out, workspace, workspace_bytes, status_word, (cudaStream_t)stream));
+                                       argmax_out, lse_out, workspace, workspace_bytes, status_word, (cudaStream_t)stream));
 }
 
 size_t b200_ffn_workspace_bytes(int64_t M, int64_t N, int64_t K, int w_is_nk, int dtype) {

@@ -141,11 +141,13 @@ int launch_gemm(const void* a, const void* b, const void* bias, const void* resi
                 int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
                 int add_gelu, int* status_word, cudaStream_t stream);
 // launch_gemm that also writes argmax_out[row] = column of the row's maximum over the (rounded) output, lowest column
-// on ties.  workspace: gemm_argmax_workspace_bytes(M, N) bytes, 16-byte aligned.  argmax_out == NULL: plain GEMM.
+// on ties, and, if lse_out is not NULL, lse_out[row] = log(sum_j exp(out[row, j])).  workspace:
+// gemm_argmax_workspace_bytes(M, N) bytes, 16-byte aligned.  argmax_out == NULL: plain GEMM.
 size_t gemm_argmax_workspace_bytes(int64_t M, int64_t N);
 int launch_gemm_argmax(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                        int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
-                       int add_gelu, int64_t* argmax_out, void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream);
+                       int add_gelu, int64_t* argmax_out, float* lse_out, void* workspace, size_t workspace_bytes, int* status_word,
+                       cudaStream_t stream);
 int launch_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L,
                      int64_t D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                      const int64_t* o_strides, float scale, int in_dtype, int out_dtype, cudaStream_t stream);

@@ -102,7 +102,15 @@ __device__ __forceinline__ TileCoord tile_coord(int64_t t, int m_tiles, int n_ti
 struct ArgmaxPartials {
   float* val;
   int* idx;
+  float* sum;  // optional: per-slice sum of exp(value - slice maximum), for the row log-sum-exp
   int64_t ld;
+};
+
+// Running (maximum, its column, sum of exp(value - maximum)) of one thread's part of an output row.
+struct RowStats {
+  float best_val;
+  int best_idx;
+  float sumexp;
 };
 
 template <typename OutT>
@@ -116,12 +124,18 @@ struct EpilogueArgs {
   // and its column, stored slice-major: amax_val[slice * amax_ld + row].  NULL = not requested.
   float* amax_val;
   int* amax_idx;
+  float* amax_sum;  // optional, same layout: sum over the slice of exp(value - slice maximum)
   int64_t amax_ld;
 };
 
 // x * sigmoid(2y), y = sqrt(2/pi) (x + 0.044715 x^3): algebraically the reference's
 // 0.5 x (1 + tanh(y)) with tanh(y) = 2 sigmoid(2y) - 1 (kernels.py:15-26 of the reference),
 // evaluated with one ex2 and one reciprocal on the special-function unit.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float gelu_fast(float x) {
   const float c0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;  // -2 sqrt(2/pi) log2(e)
   const float c1 = c0 * 0.044715f;
@@ -203,10 +217,10 @@ struct ResidualRegs {
 // `bias_s` points at this chunk's 32 fp32 bias values in shared memory (zeros when there is no bias).
 // With `stage` != 0 (TMA-store path, 16-bit output) the 64 result bytes go to this thread's row of the warp's
 // staging tile at 16-byte slots [4*half, 4*half+4) (128-byte swizzle); otherwise they are stored to global memory.
-template <typename OutT, bool GELU>
+template <typename OutT, bool GELU, int STATS>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const float* bias_s, const EpilogueArgs<OutT>& e,
                                                const uint4* res_regs, int64_t row, int col0, int64_t N, int mode, uint32_t stage,
-                                               int half, int lane, bool row_ok, bool res_staged, float& best_val, int& best_idx) {
+                                               int half, int lane, bool row_ok, bool res_staged, RowStats& st) {
   float f[32];
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
@@ -259,13 +273,27 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
       uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) w[j] = pack2<OutT>(f[2 * j], f[2 * j + 1]);
-      if (e.amax_val) {
+      if constexpr (STATS) {
         // compare what is stored (the rounded values); strict '>' keeps the lowest column among equal maxima
+        const float m_old = st.best_val;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const float2 r = unpack2<OutT>(w[j]);
-          if (col0 + 2 * j < N && r.x > best_val) best_val = r.x, best_idx = col0 + 2 * j;
-          if (col0 + 2 * j + 1 < N && r.y > best_val) best_val = r.y, best_idx = col0 + 2 * j + 1;
+          if (col0 + 2 * j < N && r.x > st.best_val) st.best_val = r.x, st.best_idx = col0 + 2 * j;
+          if (col0 + 2 * j + 1 < N && r.y > st.best_val) st.best_val = r.y, st.best_idx = col0 + 2 * j + 1;
+        }
+        if (STATS == 2 && st.best_val > -INFINITY) {
+          // online log-sum-exp: rescale what was summed against the old maximum, add this chunk
+          const float kLog2e = 1.4426950408889634f;
+          const float m2 = st.best_val * kLog2e;
+          float acc_sum = st.sumexp * ex2_approx(m_old * kLog2e - m2);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float2 r = unpack2<OutT>(w[j]);
+            if (col0 + 2 * j < N) acc_sum += ex2_approx(fmaf(r.x, kLog2e, -m2));
+            if (col0 + 2 * j + 1 < N) acc_sum += ex2_approx(fmaf(r.y, kLog2e, -m2));
+          }
+          st.sumexp = acc_sum;
         }
       }
       if (stage != 0) {
@@ -298,10 +326,19 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
       }
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-      if (e.amax_val) {
+      if constexpr (STATS) {
+        const float m_old = st.best_val;
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          if (f[j] > best_val) best_val = f[j], best_idx = col0 + j;
+          if (f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j;
+        if (STATS == 2 && st.best_val > -INFINITY) {
+          const float kLog2e = 1.4426950408889634f;
+          const float m2 = st.best_val * kLog2e;
+          float acc_sum = st.sumexp * ex2_approx(m_old * kLog2e - m2);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc_sum += ex2_approx(fmaf(f[j], kLog2e, -m2));
+          st.sumexp = acc_sum;
+        }
       }
       return;
     }
@@ -309,6 +346,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
   // element-wise tail: ragged columns, unaligned output
   OutT* orow = e.out + row * e.ld_out + col0;
   const OutT* rrow = e.residual ? e.residual + row * e.ld_res + col0 : nullptr;
+  const float m_old = st.best_val;
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
     if (col0 + j < N) {
@@ -316,12 +354,22 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
       if (rrow) v += to_float(rrow[j]);
       const OutT o = from_float<OutT>(v);
       orow[j] = o;
-      if (e.amax_val && to_float(o) > best_val) best_val = to_float(o), best_idx = col0 + j;
+      f[j] = to_float(o);
+      if (STATS && f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j;
     }
+  }
+  if (STATS == 2 && st.best_val > -INFINITY) {
+    const float kLog2e = 1.4426950408889634f;
+    const float m2 = st.best_val * kLog2e;
+    float acc_sum = st.sumexp * ex2_approx(m_old * kLog2e - m2);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < N) acc_sum += ex2_approx(fmaf(f[j], kLog2e, -m2));
+    st.sumexp = acc_sum;
   }
 }
 
-template <typename OutT, bool GELU, int CTAS>
+template <typename OutT, bool GELU, int CTAS, int STATS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res, EpilogueArgs<OutT> epi,
@@ -533,8 +581,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_half * EPI_COLS);
-      float best_val = -INFINITY;
-      int best_idx = 0;
+      RowStats stats{-INFINITY, 0, 0.f};
 #pragma unroll
       for (int c = 0; c < EPI_CHUNKS; ++c) {
         uint32_t v[32];
@@ -557,8 +604,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
           }
           if (col0 < N)
-            epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, nullptr, row, col0, N, mode, box, c & 1, lane, row_ok,
-                                       res_tma, best_val, best_idx);
+            epilogue_chunk<OutT, GELU, STATS>(v, bias_s + col_half * EPI_COLS + c * 32, epi, nullptr, row, col0, N, mode, box, c & 1, lane, row_ok,
+                                       res_tma, stats);
           if ((c & 1) == 1) {
             fence_proxy_async_smem();
             __syncwarp();
@@ -569,14 +616,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         } else if (row_ok && col0 < N) {
-          epilogue_chunk<OutT, GELU>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode, 0u,
-                                     0, lane, row_ok, false, best_val, best_idx);
+          epilogue_chunk<OutT, GELU, STATS>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode, 0u,
+                                     0, lane, row_ok, false, stats);
         }
       }
-      if (epi.amax_val && row_ok) {
+      if (STATS && row_ok) {
         const int64_t slice = (int64_t)tc.n * (BN / EPI_COLS) + col_half;
-        epi.amax_val[slice * epi.amax_ld + row] = best_val;
-        epi.amax_idx[slice * epi.amax_ld + row] = best_idx;
+        epi.amax_val[slice * epi.amax_ld + row] = stats.best_val;
+        epi.amax_idx[slice * epi.amax_ld + row] = stats.best_idx;
+        if (STATS == 2) epi.amax_sum[slice * epi.amax_ld + row] = stats.sumexp;
       }
       if (++acc == 2) {
         acc = 0;
@@ -619,14 +667,14 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t col
 }
 
 // Largest number of 2-CTA clusters of this kernel that can be resident at once (cached per instantiation).
-template <typename OutT, bool GELU>
+template <typename OutT, bool GELU, int STATS>
 static int max_pairs() {
   static std::atomic<int> cache[kMaxDevices];  // per device; stored as value + 1 so that 0 means "not asked yet"
   const int slot = device_slot();
   if (slot < 0) return 0;
   const int seen = cache[slot].load(std::memory_order_acquire);
   if (seen > 0) return seen - 1;
-  if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES) != cudaSuccess) {
+  if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, 2, STATS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES) != cudaSuccess) {
     cudaGetLastError();
     cache[slot].store(1, std::memory_order_release);
     return 0;
@@ -641,7 +689,7 @@ static int max_pairs() {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_tn_kernel<OutT, GELU, 2>, &cfg) != cudaSuccess || n < 1) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tn_kernel<OutT, GELU, 2, STATS>, &cfg) != cudaSuccess || n < 1) {
     cudaGetLastError();
     n = 0;
   }
@@ -662,7 +710,7 @@ static int make_out_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N, int64
   return r == CUDA_SUCCESS ? B200_OK : B200_ERR_CUDA;
 }
 
-template <typename OutT, bool GELU, int CTAS>
+template <typename OutT, bool GELU, int CTAS, int STATS>
 static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mr, const EpilogueArgs<OutT>& epi, int64_t M, int64_t N, int64_t K,
                           int op_dtype, int64_t groups, int* status_word, cudaStream_t stream) {
   using C = Cfg<CTAS>;
@@ -670,7 +718,7 @@ static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CU
   const int slot = device_slot();
   if (slot < 0) return B200_ERR_CUDA;
   if (!attr_set[slot].load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, CTAS, STATS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
       return B200_ERR_CUDA;
     attr_set[slot].store(true, std::memory_order_release);
   }
@@ -685,16 +733,16 @@ static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CU
   attr.val.clusterDim.x = CTAS, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tn_kernel<OutT, GELU, CTAS>, ma, mb, mo, mr, epi, M, N, K, idesc, status_word);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tn_kernel<OutT, GELU, CTAS, STATS>, ma, mb, mo, mr, epi, M, N, K, idesc, status_word);
   note_launches(1);
   return status_from_cuda(e);
 }
 
-template <typename OutT, bool GELU>
+template <typename OutT, bool GELU, int STATS>
 static int launch_typed(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K,
                         int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, const ArgmaxPartials& am, int* status_word,
                         cudaStream_t stream) {
-  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.ld};
+  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.sum, am.ld};
   CUtensorMap mo, mr;
   memset(&mo, 0, sizeof(mo));
   memset(&mr, 0, sizeof(mr));
@@ -705,7 +753,7 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
       (!residual || make_out_map(&mr, const_cast<void*>(residual), M, N, ld_res, DType<OutT>::code) == B200_OK))
     epi.tma_store = 1;
   const int64_t n_tiles = (N + BN - 1) / BN;
-  const int pairs = M > BM ? max_pairs<OutT, GELU>() : 0;
+  const int pairs = M > BM ? max_pairs<OutT, GELU, STATS>() : 0;
   CUtensorMap ma, mb;
   int st = make_map(&ma, a, M, K, lda, BM, op_dtype);
   if (st != B200_OK) return st;
@@ -713,21 +761,22 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
     st = make_map(&mb, b, N, K, ldb, Cfg<2>::B_ROWS, op_dtype);
     if (st != B200_OK) return st;
     const int64_t tiles = ((M + Cfg<2>::TILE_M - 1) / Cfg<2>::TILE_M) * n_tiles;
-    return launch_variant<OutT, GELU, 2>(ma, mb, mo, mr, epi, M, N, K, op_dtype, tiles < pairs ? tiles : pairs, status_word, stream);
+    return launch_variant<OutT, GELU, 2, STATS>(ma, mb, mo, mr, epi, M, N, K, op_dtype, tiles < pairs ? tiles : pairs, status_word, stream);
   }
   st = make_map(&mb, b, N, K, ldb, Cfg<1>::B_ROWS, op_dtype);
   if (st != B200_OK) return st;
   const int64_t tiles = ((M + BM - 1) / BM) * n_tiles;
   const int64_t sms = sm_count();
-  return launch_variant<OutT, GELU, 1>(ma, mb, mo, mr, epi, M, N, K, op_dtype, tiles < sms ? tiles : sms, status_word, stream);
+  return launch_variant<OutT, GELU, 1, STATS>(ma, mb, mo, mr, epi, M, N, K, op_dtype, tiles < sms ? tiles : sms, status_word, stream);
 }
 
 }  // namespace gemm
 
-// Row argmax from the per-slice partials the GEMM epilogue wrote: one thread per row walks the slices in column
-// order; strict '>' keeps the lowest column among equal maxima.
+// Row argmax (and optionally the row log-sum-exp) from the per-slice partials the GEMM epilogue wrote: one thread
+// per row walks the slices in column order; strict '>' keeps the lowest column among equal maxima.
 __global__ void __launch_bounds__(256)
-argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx, int64_t ld, int slices, int64_t M, int64_t* __restrict__ out) {
+argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx, const float* __restrict__ sum, int64_t ld, int slices,
+                     int64_t M, int64_t* __restrict__ out, float* __restrict__ lse_out) {
   const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= M) return;
   float best = -INFINITY;
@@ -737,27 +786,36 @@ argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx,
     if (v > best) best = v, where = idx[(int64_t)s * ld + row];
   }
   out[row] = where;
+  if (lse_out) {
+    float total = 0.f;
+    for (int s = 0; s < slices; ++s) {
+      const float v = val[(int64_t)s * ld + row];
+      if (v > -INFINITY) total += sum[(int64_t)s * ld + row] * expf(v - best);
+    }
+    lse_out[row] = best + logf(total);
+  }
 }
 
 int launch_gemm(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                 int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
                 int add_gelu, int* status_word, cudaStream_t stream) {
-  return launch_gemm_argmax(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, io_dtype, add_gelu, nullptr, nullptr, 0,
-                            status_word, stream);
+  return launch_gemm_argmax(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, io_dtype, add_gelu, nullptr, nullptr,
+                            nullptr, 0, status_word, stream);
 }
 
 size_t gemm_argmax_workspace_bytes(int64_t M, int64_t N) {
   if (M <= 0 || N <= 0) return 0;
   const int64_t slices = (N + gemm::BN - 1) / gemm::BN * (gemm::BN / gemm::EPI_COLS);
   const int64_t ld = (M + 63) / 64 * 64;
-  return (size_t)(slices * ld) * 8;
+  return (size_t)(slices * ld) * 12;  // maximum, column, sum of exponentials
 }
 
 int launch_gemm_argmax(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                        int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
-                       int add_gelu, int64_t* argmax_out, void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream) {
+                       int add_gelu, int64_t* argmax_out, float* lse_out, void* workspace, size_t workspace_bytes, int* status_word,
+                       cudaStream_t stream) {
   using namespace gemm;
-  ArgmaxPartials am{nullptr, nullptr, 0};
+  ArgmaxPartials am{nullptr, nullptr, nullptr, 0};
   if (argmax_out) {
     const size_t need = gemm_argmax_workspace_bytes(M, N);
     if (need > 0 && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))) return B200_ERR_WORKSPACE;
@@ -765,6 +823,7 @@ int launch_gemm_argmax(const void* a, const void* b, const void* bias, const voi
     const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
     am.val = static_cast<float*>(workspace);
     am.idx = reinterpret_cast<int*>(am.val + slices * am.ld);
+    if (lse_out) am.sum = am.val + 2 * slices * am.ld;
   }
   if (M == 0 || N == 0) return B200_OK;
   if (K < 1 || M < 0 || N < 0) return B200_ERR_BAD_ARGUMENT;
@@ -774,10 +833,13 @@ int launch_gemm_argmax(const void* a, const void* b, const void* bias, const voi
     return B200_ERR_ALIGNMENT;
   if (ld_out < N || (residual && ld_res < N)) return B200_ERR_BAD_ARGUMENT;
   if (M > 0x7fffffffLL - 256 || N > 0x7fffffffLL - 256 || K > 0x7fffffffLL - 64) return B200_ERR_BAD_ARGUMENT;
+  if (argmax_out && add_gelu) return B200_ERR_UNSUPPORTED;  // row statistics are built for the plain and residual epilogues only
   int st = B200_ERR_BAD_ARGUMENT;
 #define B200_GEMM_DISPATCH(T)                                                                                                              \
-  st = add_gelu ? launch_typed<T, true>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, am, status_word, stream) \
-                : launch_typed<T, false>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, am, status_word, stream)
+  st = (argmax_out && lse_out) ? launch_typed<T, false, 2>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, am, status_word, stream) \
+       : argmax_out ? launch_typed<T, false, 1>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, am, status_word, stream)  \
+       : add_gelu ? launch_typed<T, true, 0>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, am, status_word, stream)  \
+                  : launch_typed<T, false, 0>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, am, status_word, stream)
   switch (io_dtype) {
     case B200_F32: B200_GEMM_DISPATCH(float); break;
     case B200_F16: B200_GEMM_DISPATCH(__half); break;
@@ -786,7 +848,7 @@ int launch_gemm_argmax(const void* a, const void* b, const void* bias, const voi
 #undef B200_GEMM_DISPATCH
   if (st != B200_OK || !argmax_out) return st;
   const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
-  argmax_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(am.val, am.idx, am.ld, (int)slices, M, argmax_out);
+  argmax_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
   note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }

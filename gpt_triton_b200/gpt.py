@@ -151,22 +151,26 @@ class FusedGPT(_EvalOnly):
         return K.fused_layer_norm(y, self.layer_norm_weight.data, self.layer_norm_bias.data)
 
     @torch.no_grad()
-    def lm_head(self, hidden, return_argmax=False):
+    def lm_head(self, hidden, return_argmax=False, return_lse=False):
         """hidden (batch, seqlen, n_embd) -> logits (batch, seqlen, vocab_size) with the tied
         embedding matrix.  The logits buffer's row pitch is padded to a multiple of 64 elements so
         every row starts 128-byte aligned (wide stores); the result is the [..., :vocab_size] view
         of it.  ``return_argmax=True`` also returns the greedy next-token ids (batch, seqlen), taken
-        in the GEMM's epilogue (16-bit models)."""
+        in the GEMM's epilogue (16-bit models); ``return_lse=True`` additionally the row log-sum-exp
+        (batch, seqlen) float32, so that a token's cross-entropy is lse - logits[target]."""
         B, L, h = hidden.shape
         V = self.config.vocab_size
         pitch = (V + 63) // 64 * 64
         buf = torch.empty((B * L, pitch), device=hidden.device, dtype=hidden.dtype)
         w = self._operand(self.wte_weight, weight_is_nk=True)
-        if return_argmax and hidden.dtype != torch.float32:
-            _, ids = K.fused_ffn(hidden.reshape(B * L, h), w, out=buf[:, :V], return_argmax=True)
-            return buf.view(B, L, pitch)[:, :, :V], ids.view(B, L)
+        if (return_argmax or return_lse) and hidden.dtype != torch.float32:
+            res = K.fused_ffn(hidden.reshape(B * L, h), w, out=buf[:, :V], return_argmax=True, return_lse=return_lse)
+            logits = buf.view(B, L, pitch)[:, :, :V]
+            return (logits, res[1].view(B, L), res[2].view(B, L)) if return_lse else (logits, res[1].view(B, L))
         K.fused_ffn(hidden.reshape(B * L, h), w, out=buf[:, :V])
         logits = buf.view(B, L, pitch)[:, :, :V]
+        if return_lse:
+            return logits, logits.argmax(dim=-1), torch.logsumexp(logits.float(), dim=-1)
         return (logits, logits.argmax(dim=-1)) if return_argmax else logits
 
     @torch.no_grad()

@@ -136,7 +136,7 @@ def pack_weight(weight, *, weight_is_nk=False):
 
 @torch.no_grad()
 def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=0.0, *, weight_is_nk=False, out=None,
-              return_argmax=False):
+              return_argmax=False, return_lse=False):
     """z = [gelu_new](x @ weight + bias) + residual  (reference kernels.py:261-315).
 
     x (*, K); weight (K, N) -- or (N, K) with ``weight_is_nk=True``, or a PackedWeight;
@@ -144,7 +144,8 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
     preallocated (M, N) tensor whose rows are strided (last dim contiguous).  With
     ``return_argmax=True`` (needs a PackedWeight and 16-bit operands usable in place) the result
     is ``(z, ids)``, ids (M,) int64 being the argmax over each row of z (lowest column on ties),
-    produced by the GEMM's epilogue rather than by a second pass over z.
+    produced by the GEMM's epilogue rather than by a second pass over z; with ``return_lse=True`` as well,
+    ``(z, ids, lse)`` where lse (M,) float32 is log(sum_j exp(z[row, j])).
     """
     _no_dropout(dropout_prob)
     packed = weight if isinstance(weight, PackedWeight) else None
@@ -181,17 +182,19 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
     dt = dtype_code(x.dtype)
     with torch.cuda.device(dev):
         stream = stream_ptr(dev)
-        if return_argmax:
+        if return_argmax or return_lse:
             assert packed is not None and dt != _lib.F32 and K % 8 == 0 and x.data_ptr() % 16 == 0, \
                 "return_argmax needs a PackedWeight and 16-bit, 16-byte aligned activations with K % 8 == 0"
             ids = torch.empty((M,), device=dev, dtype=torch.int64)
+            lse = torch.empty((M,), device=dev, dtype=torch.float32) if return_lse else None
             need = lib.b200_gemm_argmax_workspace_bytes(M, N)
             ws = torch.empty((max(need, 16),), device=dev, dtype=torch.uint8)
             st = lib.b200_gemm_argmax(x.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, K,
                                       packed.data.stride(0), N, ld_out, dtype_code(packed.data.dtype), dt, int(bool(add_gelu)),
-                                      ids.data_ptr(), ws.data_ptr(), need, None, stream)
+                                      ids.data_ptr(), _ptr(lse), ws.data_ptr(), need, None, stream)
             check(st, "fused_ffn(argmax)")
-            return (z if out is not None else z.view((*out_shape_0, N))), ids.view(out_shape_0)
+            zz = z if out is not None else z.view((*out_shape_0, N))
+            return (zz, ids.view(out_shape_0), lse.view(out_shape_0)) if return_lse else (zz, ids.view(out_shape_0))
         if packed is not None and dt != _lib.F32 and K % 8 == 0 and x.data_ptr() % 16 == 0:
             # operands usable in place: straight to the tensor-core kernel
             st = lib.b200_gemm(x.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, K,

@@ -90,13 +90,17 @@ int b200_gemm(const void* a, const void* b, const void* bias, const void* residu
  * argmax_out[row] (int64, device) = argmax over the stored (rounded) out[row, 0..N), the lowest
  * column on ties.  Meant for the tied lm_head (gpt.py:159-161, 172-179 of the reference): greedy
  * next-token ids come out of the GEMM's epilogue instead of a second pass over the [tokens, vocab]
- * logits.  The epilogue writes per-128-column partial maxima to `workspace`
- * (b200_gemm_argmax_workspace_bytes(M, N) bytes, 16-byte aligned), a small second kernel reduces them.
+ * logits.  If lse_out (float, device, [M]) is not NULL it also receives the row log-sum-exp
+ * log(sum_j exp(out[row, j])) over the stored values, so that a token's cross-entropy is
+ * lse_out[row] - out[row, target] without reading the row again.  The epilogue writes per-128-column
+ * partial results to `workspace` (b200_gemm_argmax_workspace_bytes(M, N) bytes, 16-byte aligned), a
+ * small second kernel reduces them.
  */
 size_t b200_gemm_argmax_workspace_bytes(int64_t M, int64_t N);
 int b200_gemm_argmax(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                      int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
-                     int add_gelu, int64_t* argmax_out, void* workspace, size_t workspace_bytes, int* status_word, void* stream);
+                     int add_gelu, int64_t* argmax_out, float* lse_out, void* workspace, size_t workspace_bytes, int* status_word,
+                     void* stream);
 
 /*
  * z = [gelu_new](x @ w + bias) + residual with the reference operator's own layouts:

@@ -222,8 +222,12 @@ def test_ffn_fused_argmax(M, N, K_, dtype):
     pw = k.pack_weight(cu(w), weight_is_nk=True)
     pitch = (N + 63) // 64 * 64
     buf = torch.zeros((M, pitch), device=DEV, dtype=dtype)
-    z, ids = k.fused_ffn(cu(x), pw, out=buf[:, :N], return_argmax=True)
+    z, ids, lse = k.fused_ffn(cu(x), pw, out=buf[:, :N], return_argmax=True, return_lse=True)
     assert ids.shape == (M,) and ids.dtype == torch.int64
+    ref_lse = torch.logsumexp(z.float(), dim=1)
+    assert (lse - ref_lse).abs().max().item() < 1e-4 * max(1.0, ref_lse.abs().max().item())
+    z2, ids2 = k.fused_ffn(cu(x), pw, return_argmax=True)
+    assert torch.equal(ids2, ids) and torch.equal(z2, z)
     assert_close(z, orc.fused_ffn(x, w.T.contiguous()))
     assert torch.equal(ids.cpu(), _first_argmax(z))
     plain = k.fused_ffn(cu(x), pw)
