@@ -171,34 +171,43 @@ def run_gpu_arm(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
-    # ---- device-resident throughput ("value")
+    # ---- device-resident throughput ("value"): the forward + lm_head captured once in a CUDA graph (the library's
+    # GraphedForward) and replayed, so that host-side launch jitter on a shared box cannot starve the GPU
+    from gpt_triton_b200.gpt import GraphedForward
+
     for _ in range(args.warmup):
         model.logits(ids_dev)
+    launches_before_capture = lib.b200_launch_count()
+    fwd = GraphedForward(model, ids_dev, what="logits", warmup=1)
+    torch.cuda.synchronize()
+    launches_per_forward = (lib.b200_launch_count() - launches_before_capture) // 2  # one warm-up pass + the captured pass
+    fwd.graph.replay()
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
     barrier()
-    launches0 = lib.b200_launch_count()
     sampler.start()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
-        logits = model.logits(ids_dev)
+        fwd.graph.replay()
     end.record()
     barrier()
     clocks = sampler.stop()
-    launches = lib.b200_launch_count() - launches0
+    launches = launches_per_forward * args.steps
     ms_total = max_over_ranks(start.elapsed_time(end))
     ms_per_step = ms_total / args.steps
     value = world * tokens_per_step / (ms_per_step * 1e-3)
-    del logits
+    del fwd
 
-    # ---- end to end: pinned host ids in, argmax ids out, every step
+    # ---- end to end: pinned host ids in, argmax ids (from the lm_head epilogue) out, every step
     out_host = torch.empty((BATCH, SEQ), dtype=torch.int64).pin_memory()
+    e2e_fwd = GraphedForward(model, ids_dev, what="logits_and_next_ids", warmup=1)
     gathered = None
 
     def e2e_step():
         nonlocal gathered
-        x = ids_host.to(dev, non_blocking=True)
-        am = model.logits_and_next_ids(x)[1]  # argmax fused into the lm_head epilogue
+        e2e_fwd.static_ids.copy_(ids_host, non_blocking=True)
+        e2e_fwd.graph.replay()
+        am = e2e_fwd.outputs[1]
         if world > 1:
             parts = [torch.empty_like(am) for _ in range(world)]
             dist.all_gather(parts, am)  # 8 bytes per token cross NVLink
@@ -216,6 +225,7 @@ def run_gpu_arm(args, rank, world, local_rank):
     barrier()
     e2e_ms = max_over_ranks(start.elapsed_time(end)) / args.steps
     e2e_value = world * tokens_per_step / (e2e_ms * 1e-3)
+    del e2e_fwd
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA events around every GEMM launch
     # of further forward passes, on the stream the kernels are launched on.  The other operators are
@@ -256,21 +266,22 @@ def run_gpu_arm(args, rank, world, local_rank):
     finally:
         for name, fn in orig.items():
             setattr(K, name, fn)
-    gemm_ms = sum(s.elapsed_time(e) for *_, s, e in records)
-    gemm_flop = sum(2.0 * m * n * k for m, n, k, _, _ in records)
-    achieved_tflops = gemm_flop / (gemm_ms * 1e-3) / 1e12
-    peak_tflops = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    # Per shape, the MEDIAN launch duration (a host stall on a shared box can leave the GPU idle inside one bracket)
     by_shape = {}
     for m, n, k, s, e in records:
-        d = by_shape.setdefault((m, n, k), [0.0, 0])
-        d[0] += s.elapsed_time(e)
-        d[1] += 1
-    detail = {f"{m}x{n}x{k}": {"launches_per_step": c // probe_steps, "avg_ms": t / c, "tflops": 2.0 * m * n * k / (t / c * 1e-3) / 1e12}
-              for (m, n, k), (t, c) in by_shape.items()}
+        by_shape.setdefault((m, n, k), []).append(s.elapsed_time(e))
+    gemm_ms = sum(statistics.median(v) * len(v) for v in by_shape.values())
+    gemm_flop = sum(2.0 * m * n * k * len(v) for (m, n, k), v in by_shape.items())
+    achieved_tflops = gemm_flop / (gemm_ms * 1e-3) / 1e12
+    peak_tflops = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    detail = {f"{m}x{n}x{k}": {"launches_per_step": len(v) // probe_steps, "median_ms": statistics.median(v),
+                              "tflops": 2.0 * m * n * k / (statistics.median(v) * 1e-3) / 1e12}
+              for (m, n, k), v in by_shape.items()}
 
     breakdown = {"gemm": gemm_ms / probe_steps}
     for kind, evs in other.items():
-        breakdown[kind] = sum(s.elapsed_time(e) for s, e in evs) / probe_steps
+        times = [s.elapsed_time(e) for s, e in evs]
+        breakdown[kind] = statistics.median(times) * len(times) / probe_steps
     breakdown["unattributed"] = ms_per_step - sum(breakdown.values())
 
     flops = executed_fwd_flops(gcfg, BATCH, SEQ)
@@ -296,7 +307,7 @@ def run_gpu_arm(args, rank, world, local_rank):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ids_host.numel() * 8,
                     "d2h_bytes_per_step": out_host.numel() * 8,
                     "collective": "all_gather of argmax ids" if world > 1 else None},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "launch_mode": f"CUDA graph replay, {launches_per_forward} library kernels per forward",
             "roofline": {"kernel": "gemm_tn_kernel (tcgen05, all five GEMM shapes of the forward)", "bound": "tensor",
                          "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved_tflops / peak_tflops,
                          "peak_source": f"{peak_kind}: cuBLAS bf16 sustained",
