@@ -184,6 +184,15 @@ class FusedGPT(_EvalOnly):
         into its epilogue."""
         return self.lm_head(self.forward(x), return_argmax=True)
 
+    @torch.no_grad()
+    def token_nll(self, x, targets):
+        """ids, targets (batch, seqlen) -> per-token cross-entropy (batch, seqlen) float32:
+        lse(logits) - logits[target], the row log-sum-exp coming out of the lm_head's epilogue, so the
+        logits are read back only at the target column."""
+        logits, _, lse = self.lm_head(self.forward(x), return_argmax=True, return_lse=True)
+        picked = logits.gather(-1, targets.unsqueeze(-1)).squeeze(-1)
+        return lse - picked.float()
+
     def get_fwd_flops(self, num_tokens):
         """The reference's analytic count (gpt.py:182-196): embeddings counted as matmuls,
         attention score/value products not counted."""

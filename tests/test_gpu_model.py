@@ -163,6 +163,21 @@ def test_cuda_graph_replay_matches_eager():
         graphed(ids_a[:2])
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-3), (torch.float16, 2e-2), (torch.bfloat16, 6.3e-2)])
+def test_token_nll_vs_oracle(dtype, tol):
+    """Per-token cross-entropy from the lm_head's fused log-sum-exp against torch's cross_entropy on the oracle's
+    logits; the tolerance is that of the logits themselves (fp32: the free-running end-to-end gap)."""
+    model, cfg, sd = build_model(TINY, dtype, random_affine=True)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 1024, (3, 77), generator=g)
+    targets = torch.randint(0, 1024, (3, 77), generator=g)
+    nll = model.token_nll(ids.to(DEV), targets.to(DEV)).cpu()
+    ref_logits = orc.lm_head(sd, orc.gpt_forward(sd, cfg, ids)).float()
+    ref = torch.nn.functional.cross_entropy(ref_logits.view(-1, 1024), targets.view(-1), reduction="none").view(3, 77)
+    assert nll.dtype == torch.float32 and nll.shape == (3, 77)
+    assert (nll - ref).abs().max().item() < 2 * tol
+
+
 def test_training_mode_rejected():
     model, _, _ = build_model(TINY, torch.float32)
     model.train()
