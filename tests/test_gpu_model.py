@@ -178,6 +178,42 @@ def test_token_nll_vs_oracle(dtype, tol):
     assert (nll - ref).abs().max().item() < 2 * tol
 
 
+@pytest.mark.parametrize("dtype,atol", [(torch.float32, 5e-3), (torch.float16, 2e-2)])
+def test_converted_huggingface_model_matches_transformers(dtype, atol):
+    """What the reference's test_gpt2 checks (test.py:120-133, atol 1e-1 there), with a GPT2Model built from a
+    config and seeded instead of the downloaded checkpoint: state dict converted with
+    convert_huggingface_to_triton, loaded into FusedGPT, run on the GPU, compared with transformers' own fp32
+    forward on the CPU (an independent implementation: true fp32 matmuls, erf-free gelu_new, softmax attention).
+    The fp32 bound is the fp16 rounding of dot operands that the reference applies and transformers does not
+    (the CPU oracle differs from transformers by 2.0e-3 on these inputs)."""
+    from transformers import GPT2Config, GPT2Model
+
+    from gpt_triton_b200.gpt import FusedGPT, convert_huggingface_to_triton
+
+    torch.manual_seed(11)
+    hf_cfg = GPT2Config(vocab_size=1024, n_positions=128, n_embd=128, n_layer=2, n_head=4,
+                        resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    hf = GPT2Model(hf_cfg).eval()
+    with torch.no_grad():  # non-trivial LayerNorm affine parameters and biases
+        for name, prm in hf.named_parameters():
+            if name.endswith("bias"):
+                prm.normal_(0.0, 0.02)
+            elif "ln_" in name:
+                prm.add_(torch.randn_like(prm) * 0.1)
+    sd, cfg = convert_huggingface_to_triton(hf.state_dict(), hf_cfg)
+    model = FusedGPT(cfg)
+    model.load_state_dict(sd)
+    model = model.to(dtype).to(DEV).eval()
+    ids = torch.randint(0, 1024, (3, 100), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        ref = hf(ids).last_hidden_state
+    hidden = model(ids.to(DEV)).cpu().float()
+    assert (hidden - ref).abs().max().item() < atol
+    ref_logits = ref @ hf.wte.weight.T
+    logits = model.lm_head(model(ids.to(DEV))).cpu().float()
+    assert (logits - ref_logits).abs().max().item() < atol
+
+
 def test_training_mode_rejected():
     model, _, _ = build_model(TINY, torch.float32)
     model.train()
