@@ -29,6 +29,7 @@ SIGNATURES = {
     "b200_gemm": (c_int, [c_void_p] * 5 + [c_i64] * 7 + [c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200_gemm_argmax_workspace_bytes": (c_size_t, [c_i64, c_i64]),
     "b200_gemm_argmax": (c_int, [c_void_p] * 5 + [c_i64] * 7 + [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "b200_gemm_rowstats": (c_int, [c_void_p] * 3 + [c_i64] * 5 + [c_int, c_int] + [c_void_p] * 5 + [c_size_t, c_void_p, c_void_p]),
     "b200_ffn_workspace_bytes": (c_size_t, [c_i64, c_i64, c_i64, c_int, c_int]),
     "b200_ffn": (c_int, [c_void_p] * 5 + [c_i64] * 4 + [c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "b200_ffn_static_scratch": (c_int, [c_void_p] * 5 + [c_i64] * 4 + [c_int, c_int, c_int, c_void_p, c_void_p]),

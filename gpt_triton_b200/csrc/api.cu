@@ -33,7 +33,7 @@ const char* b200_status_string(int status) {
 
 const char* b200_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
 
-int b200_abi_version(void) { return 2; }
+int b200_abi_version(void) { return 3; }
 
 uint64_t b200_launch_count(void) { return b200::launches_so_far(); }
 
@@ -79,6 +79,14 @@ int b200_gemm_argmax(const void* a, const void* b, const void* bias, const void*
   if (!valid_dtype(io_dtype) || !argmax_out) return B200_ERR_BAD_ARGUMENT;
   return note(b200::launch_gemm_argmax(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, io_dtype, add_gelu,
                                        argmax_out, lse_out, workspace, workspace_bytes, status_word, (cudaStream_t)stream));
+}
+
+int b200_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                       int op_dtype, int round_dtype, const int64_t* targets, int64_t* argmax_out, float* lse_out,
+                       float* target_logit_out, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+  if (!valid_dtype(round_dtype)) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_gemm_rowstats(a, b, bias, M, N, K, lda, ldb, op_dtype, round_dtype, targets, argmax_out, lse_out,
+                                         target_logit_out, workspace, workspace_bytes, status_word, (cudaStream_t)stream));
 }
 
 size_t b200_ffn_workspace_bytes(int64_t M, int64_t N, int64_t K, int w_is_nk, int dtype) {

@@ -148,6 +148,9 @@ int launch_gemm_argmax(const void* a, const void* b, const void* bias, const voi
                        int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
                        int add_gelu, int64_t* argmax_out, float* lse_out, void* workspace, size_t workspace_bytes, int* status_word,
                        cudaStream_t stream);
+int launch_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                         int op_dtype, int round_dtype, const int64_t* targets, int64_t* argmax_out, float* lse_out, float* target_out,
+                         void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream);
 int launch_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L,
                      int64_t D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                      const int64_t* o_strides, float scale, int in_dtype, int out_dtype, cudaStream_t stream);

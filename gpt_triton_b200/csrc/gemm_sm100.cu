@@ -126,6 +126,9 @@ struct EpilogueArgs {
   int* amax_idx;
   float* amax_sum;  // optional, same layout: sum over the slice of exp(value - slice maximum)
   int64_t amax_ld;
+  // Statistics-only launches: optional per-row target column and where that row's (rounded) value at it goes.
+  const int64_t* targets;
+  float* target_val;
 };
 
 // x * sigmoid(2y), y = sqrt(2/pi) (x + 0.044715 x^3): algebraically the reference's
@@ -369,6 +372,49 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
   }
 }
 
+// Statistics-only epilogue (nothing is stored): the 32 values a thread would have written, rounded to the output
+// type as the storing epilogue rounds them, update the row's running maximum / column / sum of exponentials, and
+// the value at column `tgt` (if it falls into this chunk) is picked out.
+template <typename OutT>
+__device__ __forceinline__ void stats_only_chunk(const uint32_t (&acc)[32], const float* bias_s, int col0, int64_t N, int tgt, RowStats& st,
+                                                 float& picked) {
+  float f[32];
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 b = *reinterpret_cast<const float4*>(bias_s + j);
+    f[j] = __uint_as_float(acc[j]) + b.x;
+    f[j + 1] = __uint_as_float(acc[j + 1]) + b.y;
+    f[j + 2] = __uint_as_float(acc[j + 2]) + b.z;
+    f[j + 3] = __uint_as_float(acc[j + 3]) + b.w;
+  }
+  if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const float2 r = unpack2<OutT>(pack2<OutT>(f[j], f[j + 1]));
+      f[j] = r.x, f[j + 1] = r.y;
+    }
+  }
+  const float m_old = st.best_val;
+  const bool full = col0 + 32 <= N;
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if ((full || col0 + j < N) && f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j;  // strict '>': lowest column wins ties
+  if (st.best_val > -INFINITY) {
+    const float kLog2e = 1.4426950408889634f;
+    const float m2 = st.best_val * kLog2e;
+    float acc_sum = st.sumexp * ex2_approx(m_old * kLog2e - m2);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || col0 + j < N) acc_sum += ex2_approx(fmaf(f[j], kLog2e, -m2));
+    st.sumexp = acc_sum;
+  }
+  if (tgt >= col0 && tgt < col0 + 32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j == tgt) picked = f[j];
+  }
+}
+
 template <typename OutT, bool GELU, int CTAS, int STATS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -530,7 +576,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int mode = STORE_SCALAR;
     if (((out_al | res_al) & 15) == 0) mode = (esz == 2 && (out_al & 31) == 0) ? STORE_32B : STORE_16B;
     const uint32_t acc_empty_base = CTAS == 2 ? mapa_shared(bar_acc_empty, 0) : bar_acc_empty;
-    const bool use_tma = esz == 2 && epi.tma_store != 0;
+    const bool use_tma = STATS != 3 && esz == 2 && epi.tma_store != 0;
     const bool res_tma = use_tma && epi.residual != nullptr;  // (the host only sets tma_store when the residual can be mapped too)
     const uint32_t stage_addr = use_tma ? smem_epi + (uint32_t)(warp - 2) * EPI_WARP_STAGE_BYTES : 0u;
     const uint32_t my_res_bar = bar_res + 8 * (uint32_t)(warp - 2);
@@ -582,6 +628,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_half * EPI_COLS);
       RowStats stats{-INFINITY, 0, 0.f};
+      float picked = 0.f;
+      int tgt = -1;
+      if constexpr (STATS == 3) {
+        if (epi.targets && row_ok) {
+          const int64_t t64 = epi.targets[row];
+          tgt = (t64 >= col_base && t64 < col_base + EPI_COLS) ? (int)t64 : -1;
+        }
+      }
 #pragma unroll
       for (int c = 0; c < EPI_CHUNKS; ++c) {
         uint32_t v[32];
@@ -596,7 +650,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
         const int col0 = col_base + c * 32;
-        if (use_tma) {
+        if constexpr (STATS == 3) {
+          if (row_ok && col0 < N) stats_only_chunk<OutT>(v, bias_s + col_half * EPI_COLS + c * 32, col0, N, tgt, stats, picked);
+        } else if (use_tma) {
           const uint32_t box = stage_addr + (uint32_t)(c >> 1) * EPI_BOX_BYTES;
           if (!res_tma && (c & 1) == 0) {
             // about to overwrite this box: its store of the previous tile is the second most recent bulk group
@@ -624,7 +680,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int64_t slice = (int64_t)tc.n * (BN / EPI_COLS) + col_half;
         epi.amax_val[slice * epi.amax_ld + row] = stats.best_val;
         epi.amax_idx[slice * epi.amax_ld + row] = stats.best_idx;
-        if (STATS == 2) epi.amax_sum[slice * epi.amax_ld + row] = stats.sumexp;
+        if (STATS >= 2) epi.amax_sum[slice * epi.amax_ld + row] = stats.sumexp;
+        if (STATS == 3 && tgt >= 0 && tgt < N) epi.target_val[row] = picked;
       }
       if (++acc == 2) {
         acc = 0;
@@ -741,13 +798,13 @@ static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CU
 template <typename OutT, bool GELU, int STATS>
 static int launch_typed(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K,
                         int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, const ArgmaxPartials& am, int* status_word,
-                        cudaStream_t stream) {
-  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.sum, am.ld};
+                        cudaStream_t stream, const int64_t* targets = nullptr, float* target_val = nullptr) {
+  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.sum, am.ld, targets, target_val};
   CUtensorMap mo, mr;
   memset(&mo, 0, sizeof(mo));
   memset(&mr, 0, sizeof(mr));
   // TMA epilogue: 16-bit output (and residual, if any) with 16-byte aligned base and pitch
-  if (sizeof(OutT) == 2 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_out % 8 == 0 &&
+  if (STATS != 3 && sizeof(OutT) == 2 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_out % 8 == 0 &&
       (!residual || ((reinterpret_cast<uintptr_t>(residual) & 15) == 0 && ld_res % 8 == 0)) &&
       make_out_map(&mo, out, M, N, ld_out, DType<OutT>::code) == B200_OK &&
       (!residual || make_out_map(&mr, const_cast<void*>(residual), M, N, ld_res, DType<OutT>::code) == B200_OK))
@@ -848,6 +905,40 @@ int launch_gemm_argmax(const void* a, const void* b, const void* bias, const voi
 #undef B200_GEMM_DISPATCH
   if (st != B200_OK || !argmax_out) return st;
   const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
+  argmax_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
+  note_launches(1);
+  return status_from_cuda(cudaGetLastError());
+}
+
+// Row statistics of A B^T (+ bias) without storing the product: argmax, log-sum-exp and, optionally, the value at a
+// per-row target column, all taken from the values as they would be rounded to `round_dtype` (fp16 or bf16).
+int launch_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                         int op_dtype, int round_dtype, const int64_t* targets, int64_t* argmax_out, float* lse_out, float* target_out,
+                         void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream) {
+  using namespace gemm;
+  if (!argmax_out || !lse_out || (targets != nullptr) != (target_out != nullptr)) return B200_ERR_BAD_ARGUMENT;
+  if (K < 1 || M < 0 || N < 0) return B200_ERR_BAD_ARGUMENT;
+  if (M == 0 || N == 0) return B200_OK;
+  if (op_dtype != B200_F16 && op_dtype != B200_BF16) return B200_ERR_BAD_ARGUMENT;
+  if (round_dtype != B200_F16 && round_dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
+  if (!a || !b) return B200_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || lda % 8 || ldb % 8 || lda < K || ldb < K)
+    return B200_ERR_ALIGNMENT;
+  if (M > 0x7fffffffLL - 256 || N > 0x7fffffffLL - 256 || K > 0x7fffffffLL - 64) return B200_ERR_BAD_ARGUMENT;
+  const size_t need = gemm_argmax_workspace_bytes(M, N);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return B200_ERR_WORKSPACE;
+  ArgmaxPartials am;
+  am.ld = (M + 63) / 64 * 64;
+  const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
+  am.val = static_cast<float*>(workspace);
+  am.idx = reinterpret_cast<int*>(am.val + slices * am.ld);
+  am.sum = am.val + 2 * slices * am.ld;
+  int st;
+  if (round_dtype == B200_F16)
+    st = launch_typed<__half, false, 3>(a, b, bias, nullptr, nullptr, M, N, K, lda, ldb, 0, N, op_dtype, am, status_word, stream, targets, target_out);
+  else
+    st = launch_typed<__nv_bfloat16, false, 3>(a, b, bias, nullptr, nullptr, M, N, K, lda, ldb, 0, N, op_dtype, am, status_word, stream, targets, target_out);
+  if (st != B200_OK) return st;
   argmax_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
   note_launches(1);
   return status_from_cuda(cudaGetLastError());

@@ -185,13 +185,29 @@ class FusedGPT(_EvalOnly):
         return self.lm_head(self.forward(x), return_argmax=True)
 
     @torch.no_grad()
+    def next_ids(self, x):
+        """ids (batch, seqlen) -> greedy next-token ids (batch, seqlen): forward(), then the tied lm_head reduced to its
+        row argmax inside the GEMM's epilogue; the (tokens, vocab) logits are never written (16-bit models; fp32 models
+        go through the logits)."""
+        hidden = self.forward(x)
+        if hidden.dtype == torch.float32:
+            return self.lm_head(hidden, return_argmax=True)[1]
+        B, L, h = hidden.shape
+        return K.ffn_row_statistics(hidden.reshape(B * L, h), self._operand(self.wte_weight, weight_is_nk=True))[0].view(B, L)
+
+    @torch.no_grad()
     def token_nll(self, x, targets):
-        """ids, targets (batch, seqlen) -> per-token cross-entropy (batch, seqlen) float32:
-        lse(logits) - logits[target], the row log-sum-exp coming out of the lm_head's epilogue, so the
-        logits are read back only at the target column."""
-        logits, _, lse = self.lm_head(self.forward(x), return_argmax=True, return_lse=True)
-        picked = logits.gather(-1, targets.unsqueeze(-1)).squeeze(-1)
-        return lse - picked.float()
+        """ids, targets (batch, seqlen) -> per-token cross-entropy (batch, seqlen) float32 =
+        lse(logits) - logits[target], over the logits as the lm_head would round them.  16-bit models take both terms
+        out of the lm_head GEMM's epilogue without writing the logits; fp32 models go through the logits."""
+        hidden = self.forward(x)
+        if hidden.dtype == torch.float32:
+            logits, _, lse = self.lm_head(hidden, return_argmax=True, return_lse=True)
+            return lse - logits.gather(-1, targets.unsqueeze(-1)).squeeze(-1)
+        B, L, h = hidden.shape
+        w = self._operand(self.wte_weight, weight_is_nk=True)
+        _, lse, picked = K.ffn_row_statistics(hidden.reshape(B * L, h), w, targets=targets.reshape(B * L).contiguous())
+        return (lse - picked).view(B, L)
 
     def get_fwd_flops(self, num_tokens):
         """The reference's analytic count (gpt.py:182-196): embeddings counted as matmuls,

@@ -222,6 +222,44 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
     return z.view((*out_shape_0, N))
 
 
+@torch.no_grad()
+def ffn_row_statistics(x, weight, bias=None, targets=None):
+    """Row statistics of z = x @ weight (+ bias) without materialising z (no counterpart in the reference, whose
+    lm_head is commented out, gpt.py:172-179): ``(ids, lse, target_value)`` with ids (*,) int64 the argmax of each
+    row (lowest column on ties), lse (*,) float32 = log(sum_j exp(z[row, j])) and, when ``targets`` (*,) int64 is
+    given, target_value (*,) float32 = z[row, targets[row]] (NaN where the target is outside [0, N); else None) --
+    all over z rounded to x.dtype exactly as fused_ffn would store it.  ``weight`` must be a PackedWeight, x 16-bit
+    with K % 8 == 0."""
+    assert isinstance(weight, PackedWeight), "ffn_row_statistics needs a PackedWeight"
+    require_cuda(x, bias, targets)
+    lead = x.shape[:-1]
+    x = x.view((-1, x.shape[-1]))
+    M, K = x.shape
+    N = weight.N
+    dt = dtype_code(x.dtype)
+    assert K == weight.K and weight.storage_dtype == x.dtype and x.is_contiguous()
+    assert dt != _lib.F32 and K % 8 == 0 and x.data_ptr() % 16 == 0, "16-bit, 16-byte aligned activations with K % 8 == 0 only"
+    dev = _same_device(x, weight.data, bias, targets)
+    if bias is not None:
+        assert bias.is_contiguous() and bias.shape[0] == N and bias.dtype == x.dtype
+    ids = torch.empty((M,), device=dev, dtype=torch.int64)
+    lse = torch.empty((M,), device=dev, dtype=torch.float32)
+    picked = None
+    if targets is not None:
+        targets = targets.reshape(-1)
+        assert targets.dtype == torch.int64 and targets.is_contiguous() and targets.shape[0] == M
+        picked = torch.full((M,), float("nan"), device=dev, dtype=torch.float32)
+    lib = _lib.load()
+    need = lib.b200_gemm_argmax_workspace_bytes(M, N)
+    ws = torch.empty((max(need, 16),), device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        st = lib.b200_gemm_rowstats(x.data_ptr(), weight.data.data_ptr(), _ptr(bias), M, N, K, K, weight.data.stride(0),
+                                    dtype_code(weight.data.dtype), dt, _ptr(targets), ids.data_ptr(), lse.data_ptr(), _ptr(picked),
+                                    ws.data_ptr(), need, None, stream_ptr(dev))
+    check(st, "ffn_row_statistics")
+    return ids.view(lead), lse.view(lead), (picked.view(lead) if picked is not None else None)
+
+
 # ----------------------------------------------------------------------------- qkv split
 @torch.no_grad()
 def matmul_and_split_qkv(x, weight, bias, num_heads):

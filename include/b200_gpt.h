@@ -35,7 +35,7 @@ enum {
 const char* b200_status_string(int status);
 /* cudaGetErrorString of the last failing CUDA call made by this library on this thread. */
 const char* b200_last_cuda_error(void);
-/* ABI version of this header; bumped on any signature change. */
+/* ABI version of this header (3); bumped when a signature changes or an entry point is added. */
 int b200_abi_version(void);
 /* Number of kernels this library has launched in this process so far (all entry points). */
 uint64_t b200_launch_count(void);
@@ -101,6 +101,19 @@ int b200_gemm_argmax(const void* a, const void* b, const void* bias, const void*
                      int64_t K, int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype,
                      int add_gelu, int64_t* argmax_out, float* lse_out, void* workspace, size_t workspace_bytes, int* status_word,
                      void* stream);
+
+/*
+ * Row statistics of the product without the product: for logits[M,N] = A[M,K] . B[N,K]^T (+ bias[N]) rounded to
+ * round_dtype (F16 or BF16) exactly as b200_gemm would store them, returns per row argmax_out (int64, lowest column
+ * on ties), lse_out (float, log-sum-exp over the rounded values) and, if `targets` (int64 [M], device) is not NULL,
+ * target_logit_out[row] = logits[row, targets[row]] (float; rows whose target lies outside [0, N) are left
+ * untouched).  Nothing of size M x N touches memory: the tied lm_head (gpt.py:159-161, 172-179 of the reference)
+ * for greedy next-token ids or per-token cross-entropy (lse - target logit) without the [tokens, vocab] tensor.
+ * bias is of round_dtype or NULL.  Workspace: b200_gemm_argmax_workspace_bytes(M, N) bytes, 16-byte aligned.
+ */
+int b200_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                       int op_dtype, int round_dtype, const int64_t* targets, int64_t* argmax_out, float* lse_out,
+                       float* target_logit_out, void* workspace, size_t workspace_bytes, int* status_word, void* stream);
 
 /*
  * z = [gelu_new](x @ w + bias) + residual with the reference operator's own layouts:

@@ -32,7 +32,7 @@ def test_library_builds_and_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/b200_gpt.h but not exported"
     assert sorted(_lib.SIGNATURES) == names, "ctypes signature table and header disagree"
     bound = _lib.load()
-    assert bound.b200_abi_version() == 2
+    assert bound.b200_abi_version() == 3
     assert bound.b200_status_string(0) == b"ok"
     assert bound.b200_status_string(6) == b"a kernel abandoned a bounded wait"
 

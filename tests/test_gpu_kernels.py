@@ -234,6 +234,53 @@ def test_ffn_fused_argmax(M, N, K_, dtype):
     assert torch.equal(plain, z)  # asking for the argmax does not change the output
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K_,use_bias", [(300, 1001, 128, False), (1, 8, 8, True), (1000, 50257, 64, False), (129, 256, 72, True),
+                                             (513, 700, 768, True)])
+def test_ffn_row_statistics_without_the_product(M, N, K_, use_bias, dtype):
+    """Argmax, log-sum-exp and the value at a per-row target column, taken in the GEMM epilogue with nothing of
+    size M x N written: bit-identical to the same statistics of the product that fused_ffn stores (ties, ragged N,
+    vocabulary-sized N, bias), NaN where a target is out of range."""
+    k = K()
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = (torch.randn((M, K_), generator=g) * 0.5).to(dtype)
+    w = torch.randint(-2, 3, (N, K_), generator=g).to(dtype) * 0.25  # coarse weights -> many exact ties
+    b = torch.randn((N,), generator=g).to(dtype) if use_bias else None
+    tgt = torch.randint(0, N, (M,), generator=g)
+    tgt[0] = N - 1
+    if M > 2:
+        tgt[1], tgt[2] = -1, N  # outside [0, N)
+    pw = k.pack_weight(cu(w), weight_is_nk=True)
+    z, ids_ref, lse_ref = k.fused_ffn(cu(x), pw, bias=cu(b), return_argmax=True, return_lse=True)
+    ids, lse, picked = k.ffn_row_statistics(cu(x), pw, bias=cu(b), targets=cu(tgt))
+    assert ids.shape == (M,) and ids.dtype == torch.int64 and lse.dtype == torch.float32 and picked.dtype == torch.float32
+    assert torch.equal(ids, ids_ref)
+    assert torch.equal(ids.cpu(), _first_argmax(z))
+    assert (lse - lse_ref).abs().max().item() <= 1e-6 * max(1.0, lse_ref.abs().max().item())
+    ok = (tgt >= 0) & (tgt < N)
+    want = z.float().cpu().gather(1, tgt.clamp(0, N - 1)[:, None])[:, 0]
+    assert torch.equal(picked.cpu()[ok], want[ok])
+    assert torch.isnan(picked.cpu()[~ok]).all()
+    ids2, lse2, none = k.ffn_row_statistics(cu(x), pw, bias=cu(b))
+    assert none is None and torch.equal(ids2, ids) and torch.equal(lse2, lse)
+    # leading dimensions are kept
+    if M % 3 == 0:
+        i3, l3, p3 = k.ffn_row_statistics(cu(x).view(3, M // 3, K_), pw, bias=cu(b), targets=cu(tgt).view(3, M // 3))
+        assert i3.shape == (3, M // 3) and torch.equal(i3.view(-1), ids) and torch.equal(p3.view(-1)[cu(ok)], picked[cu(ok)])
+
+
+def test_ffn_row_statistics_asserts():
+    k = K()
+    x = torch.zeros((4, 64), device=DEV, dtype=torch.float16)
+    w = torch.zeros((64, 32), device=DEV, dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        k.ffn_row_statistics(x, w)  # needs a PackedWeight
+    with pytest.raises(AssertionError):
+        k.ffn_row_statistics(x.float(), k.pack_weight(w.float()))  # 16-bit only
+    with pytest.raises(AssertionError):
+        k.ffn_row_statistics(x, k.pack_weight(w), targets=torch.zeros((3,), device=DEV, dtype=torch.int64))
+
+
 def test_ffn_full_size_fp16_gelu():
     """The kernel-sweep GEMM: M=153600, K=768, N=3072, fp16, bias + GELU.  Oracle parity on a row
     sample, and row independence: the same rows computed as a small problem give the same bits."""

@@ -176,6 +176,11 @@ def test_token_nll_vs_oracle(dtype, tol):
     ref = torch.nn.functional.cross_entropy(ref_logits.view(-1, 1024), targets.view(-1), reduction="none").view(3, 77)
     assert nll.dtype == torch.float32 and nll.shape == (3, 77)
     assert (nll - ref).abs().max().item() < 2 * tol
+    # the same numbers as from the materialised logits, and the greedy ids without them
+    logits, ids_ref, lse = model.lm_head(model(ids.to(DEV)), return_argmax=True, return_lse=True)
+    via_logits = (lse - logits.gather(-1, targets.to(DEV)[..., None])[..., 0].float()).cpu()
+    assert (nll - via_logits).abs().max().item() < 1e-5
+    assert torch.equal(model.next_ids(ids.to(DEV)), ids_ref)
 
 
 @pytest.mark.parametrize("dtype,atol", [(torch.float32, 5e-3), (torch.float16, 2e-2)])
