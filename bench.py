@@ -227,6 +227,19 @@ def run_gpu_arm(args, rank, world, local_rank):
     e2e_value = world * tokens_per_step / (e2e_ms * 1e-3)
     del e2e_fwd
 
+    # ---- for information: the same forward with the lm_head reduced to its row argmax inside the GEMM epilogue
+    # (FusedGPT.next_ids: the [tokens, vocab] logits are never written); not the headline workload
+    ids_fwd = GraphedForward(model, ids_dev, what="next_ids", warmup=1)
+    ids_fwd.graph.replay()
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        ids_fwd.graph.replay()
+    end.record()
+    barrier()
+    ids_only_ms = max_over_ranks(start.elapsed_time(end)) / args.steps
+    del ids_fwd
+
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA events around every GEMM launch
     # of further forward passes, on the stream the kernels are launched on.  The other operators are
     # bracketed the same way to give the per-step breakdown.
@@ -307,6 +320,8 @@ def run_gpu_arm(args, rank, world, local_rank):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ids_host.numel() * 8,
                     "d2h_bytes_per_step": out_host.numel() * 8,
                     "collective": "all_gather of argmax ids" if world > 1 else None},
+            "next_ids_only": {"value": world * tokens_per_step / (ids_only_ms * 1e-3), "unit": "tokens/s", "ms_per_step": ids_only_ms,
+                              "note": "same forward, greedy ids out of the lm_head epilogue, logits not written; informational"},
             "gpu_launches": int(launches), "launch_mode": f"CUDA graph replay, {launches_per_forward} library kernels per forward",
             "roofline": {"kernel": "gemm_tn_kernel (tcgen05, all five GEMM shapes of the forward)", "bound": "tensor",
                          "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved_tflops / peak_tflops,

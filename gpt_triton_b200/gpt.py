@@ -224,11 +224,11 @@ class GraphedForward:
 
     The 87 kernel launches of a 12-layer forward cost the host a few milliseconds; at small batches that is
     more than the GPU needs (8 x 300 tokens: 2.9 ms eager, 1.4 ms replayed on a B200).  ``what`` selects the
-    captured method: "forward" (hidden state), "logits" or "logits_and_next_ids".  The results are static
+    captured method: "forward" (hidden state), "logits", "logits_and_next_ids" or "next_ids".  The results are static
     buffers that every call overwrites; clone them to keep them."""
 
     def __init__(self, model, example_ids, what="logits", warmup=3):
-        assert what in ("forward", "logits", "logits_and_next_ids")
+        assert what in ("forward", "logits", "logits_and_next_ids", "next_ids")
         self._fn = getattr(model, what)
         self.static_ids = example_ids.clone()
         # warm-up on a side stream: first calls set kernel attributes, pack weights and fill the allocator's pool
