@@ -111,6 +111,7 @@ struct RowStats {
   float best_val;
   int best_idx;
   float sumexp;
+  int pending_col0;  // >= 0: best_val was found in the staged 32-column chunk starting here; its column is looked up once per tile
 };
 
 template <typename OutT>
@@ -152,13 +153,16 @@ __device__ __forceinline__ float gelu_fast(float x) {
 // The same function with a single special-function operation: 0.5 x (1 + tanh(y)) on the hardware tanh.
 // Its 2^-11 relative error in tanh is at most half a 16-bit ulp of the result, so it is used only when the
 // output is rounded to fp16/bf16; fp32 outputs take gelu_fast.
-__device__ __forceinline__ float gelu_tanh_approx(float x) {
+// Two values at once: the multiplies and fused multiply-adds are packed fp32x2 instructions (rounded as the
+// scalar forms).
+__device__ __forceinline__ float2 gelu_tanh_approx2(float2 x) {
   const float c0 = 0.7978845608028654f, c1 = 0.7978845608028654f * 0.044715f;
-  const float y = x * fmaf(x * x, c1, c0);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(y));
-  const float h = 0.5f * x;
-  return fmaf(h, t, h);
+  const float2 y = __fmul2_rn(x, __ffma2_rn(__fmul2_rn(x, x), make_float2(c1, c1), make_float2(c0, c0)));
+  float2 t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t.x) : "f"(y.x));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t.y) : "f"(y.y));
+  const float2 h = __fmul2_rn(x, make_float2(0.5f, 0.5f));
+  return __ffma2_rn(h, t, h);
 }
 
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&v)[8]) {
@@ -207,6 +211,43 @@ __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
   return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
 }
 
+// Element-wise maximum of two packed 16-bit pairs (a NaN loses against a number).
+template <typename OutT>
+__device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b);
+template <>
+__device__ __forceinline__ uint32_t max2<__half>(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+template <>
+__device__ __forceinline__ uint32_t max2<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Lowest column of this thread's staged 32-column chunk (64 bytes of its row in a 128-byte-swizzled staging box,
+// 16-byte slots [4*half, 4*half+4)) whose value equals `best`; 0 if there is none.
+template <typename OutT>
+__device__ __forceinline__ int find_staged_column(uint32_t box, int half, int lane, float best) {
+  const uint32_t rowaddr = box + (uint32_t)lane * 128u;
+  const uint32_t sw = (uint32_t)(lane & 7);
+  int idx = 0;
+#pragma unroll
+  for (int g = 3; g >= 0; --g) {
+    uint32_t q[4];
+    ld_shared_v4(rowaddr + ((((uint32_t)(half * 4 + g)) ^ sw) << 4), q);
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      const float2 r = unpack2<OutT>(q[j]);
+      if (r.y == best) idx = g * 8 + 2 * j + 1;
+      if (r.x == best) idx = g * 8 + 2 * j;
+    }
+  }
+  return idx;
+}
+
 // How a thread may store its 32-column pieces of an output row.
 enum StoreMode { STORE_SCALAR = 0, STORE_16B = 1, STORE_32B = 2 };
 
@@ -224,18 +265,32 @@ template <typename OutT, bool GELU, int STATS>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const float* bias_s, const EpilogueArgs<OutT>& e,
                                                const uint4* res_regs, int64_t row, int col0, int64_t N, int mode, uint32_t stage,
                                                int half, int lane, bool row_ok, bool res_staged, RowStats& st) {
+  // Two columns per instruction where the hardware has packed fp32 forms (add, mul, fma: same roundings as the
+  // scalar ones); no bias, no add.
   float f[32];
+  if (e.bias) {
 #pragma unroll
-  for (int j = 0; j < 32; j += 4) {
-    const float4 b = *reinterpret_cast<const float4*>(bias_s + j);
-    f[j] = __uint_as_float(acc[j]) + b.x;
-    f[j + 1] = __uint_as_float(acc[j + 1]) + b.y;
-    f[j + 2] = __uint_as_float(acc[j + 2]) + b.z;
-    f[j + 3] = __uint_as_float(acc[j + 3]) + b.w;
+    for (int j = 0; j < 32; j += 4) {
+      const float4 b = *reinterpret_cast<const float4*>(bias_s + j);
+      const float2 lo = __fadd2_rn(make_float2(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1])), make_float2(b.x, b.y));
+      const float2 hi = __fadd2_rn(make_float2(__uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3])), make_float2(b.z, b.w));
+      f[j] = lo.x, f[j + 1] = lo.y, f[j + 2] = hi.x, f[j + 3] = hi.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(acc[j]);
   }
   if (GELU) {
+    if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) f[j] = sizeof(OutT) == 2 ? gelu_tanh_approx(f[j]) : gelu_fast(f[j]);
+      for (int j = 0; j < 32; j += 2) {
+        const float2 g = gelu_tanh_approx2(make_float2(f[j], f[j + 1]));
+        f[j] = g.x, f[j + 1] = g.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = gelu_fast(f[j]);
+    }
   }
   const bool full = col0 + 32 <= N;
   if constexpr (sizeof(OutT) == 2) {
@@ -279,11 +334,22 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
       if constexpr (STATS) {
         // compare what is stored (the rounded values); strict '>' keeps the lowest column among equal maxima
         const float m_old = st.best_val;
+        if (stage != 0 && full) {
+          // chunk maximum with packed 16-bit max instructions; which column it sits in is looked up later, once per
+          // tile, in the staging tile (find_staged_column), and only for the chunk that won
+          uint32_t m = w[0];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float2 r = unpack2<OutT>(w[j]);
-          if (col0 + 2 * j < N && r.x > st.best_val) st.best_val = r.x, st.best_idx = col0 + 2 * j;
-          if (col0 + 2 * j + 1 < N && r.y > st.best_val) st.best_val = r.y, st.best_idx = col0 + 2 * j + 1;
+          for (int j = 1; j < 16; ++j) m = max2<OutT>(m, w[j]);
+          const float2 mm = unpack2<OutT>(m);
+          const float cm = fmaxf(mm.x, mm.y);
+          if (cm > st.best_val) st.best_val = cm, st.pending_col0 = col0;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float2 r = unpack2<OutT>(w[j]);
+            if (col0 + 2 * j < N && r.x > st.best_val) st.best_val = r.x, st.best_idx = col0 + 2 * j, st.pending_col0 = -1;
+            if (col0 + 2 * j + 1 < N && r.y > st.best_val) st.best_val = r.y, st.best_idx = col0 + 2 * j + 1, st.pending_col0 = -1;
+          }
         }
         if (STATS == 2 && st.best_val > -INFINITY) {
           // online log-sum-exp: rescale what was summed against the old maximum, add this chunk
@@ -333,7 +399,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
         const float m_old = st.best_val;
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          if (f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j;
+          if (f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j, st.pending_col0 = -1;
         if (STATS == 2 && st.best_val > -INFINITY) {
           const float kLog2e = 1.4426950408889634f;
           const float m2 = st.best_val * kLog2e;
@@ -358,7 +424,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
       const OutT o = from_float<OutT>(v);
       orow[j] = o;
       f[j] = to_float(o);
-      if (STATS && f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j;
+      if (STATS && f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j, st.pending_col0 = -1;
     }
   }
   if (STATS == 2 && st.best_val > -INFINITY) {
@@ -376,16 +442,21 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
 // type as the storing epilogue rounds them, update the row's running maximum / column / sum of exponentials, and
 // the value at column `tgt` (if it falls into this chunk) is picked out.
 template <typename OutT>
-__device__ __forceinline__ void stats_only_chunk(const uint32_t (&acc)[32], const float* bias_s, int col0, int64_t N, int tgt, RowStats& st,
-                                                 float& picked) {
+__device__ __forceinline__ void stats_only_chunk(const uint32_t (&acc)[32], const float* bias_s, bool has_bias, int col0, int64_t N, int tgt,
+                                                 RowStats& st, float& picked) {
   float f[32];
+  if (has_bias) {
 #pragma unroll
-  for (int j = 0; j < 32; j += 4) {
-    const float4 b = *reinterpret_cast<const float4*>(bias_s + j);
-    f[j] = __uint_as_float(acc[j]) + b.x;
-    f[j + 1] = __uint_as_float(acc[j + 1]) + b.y;
-    f[j + 2] = __uint_as_float(acc[j + 2]) + b.z;
-    f[j + 3] = __uint_as_float(acc[j + 3]) + b.w;
+    for (int j = 0; j < 32; j += 4) {
+      const float4 b = *reinterpret_cast<const float4*>(bias_s + j);
+      f[j] = __uint_as_float(acc[j]) + b.x;
+      f[j + 1] = __uint_as_float(acc[j + 1]) + b.y;
+      f[j + 2] = __uint_as_float(acc[j + 2]) + b.z;
+      f[j + 3] = __uint_as_float(acc[j + 3]) + b.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(acc[j]);
   }
   if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
@@ -398,7 +469,7 @@ __device__ __forceinline__ void stats_only_chunk(const uint32_t (&acc)[32], cons
   const bool full = col0 + 32 <= N;
 #pragma unroll
   for (int j = 0; j < 32; ++j)
-    if ((full || col0 + j < N) && f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j;  // strict '>': lowest column wins ties
+    if ((full || col0 + j < N) && f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j, st.pending_col0 = -1;  // strict '>': lowest column wins ties
   if (st.best_val > -INFINITY) {
     const float kLog2e = 1.4426950408889634f;
     const float m2 = st.best_val * kLog2e;
@@ -627,7 +698,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_half * EPI_COLS);
-      RowStats stats{-INFINITY, 0, 0.f};
+      RowStats stats{-INFINITY, 0, 0.f, -1};
       float picked = 0.f;
       int tgt = -1;
       if constexpr (STATS == 3) {
@@ -651,7 +722,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         const int col0 = col_base + c * 32;
         if constexpr (STATS == 3) {
-          if (row_ok && col0 < N) stats_only_chunk<OutT>(v, bias_s + col_half * EPI_COLS + c * 32, col0, N, tgt, stats, picked);
+          if (row_ok && col0 < N) stats_only_chunk<OutT>(v, bias_s + col_half * EPI_COLS + c * 32, epi.bias != nullptr, col0, N, tgt, stats, picked);
         } else if (use_tma) {
           const uint32_t box = stage_addr + (uint32_t)(c >> 1) * EPI_BOX_BYTES;
           if (!res_tma && (c & 1) == 0) {
@@ -674,6 +745,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         } else if (row_ok && col0 < N) {
           epilogue_chunk<OutT, GELU, STATS>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode, 0u,
                                      0, lane, row_ok, false, stats);
+        }
+      }
+      if constexpr (STATS == 1 || STATS == 2) {
+        if (stats.pending_col0 >= 0) {
+          // the winning chunk still sits in this warp's staging boxes (nothing overwrites them before the next tile)
+          const int c = (stats.pending_col0 - col_base) >> 5;
+          stats.best_idx = stats.pending_col0 +
+                           find_staged_column<OutT>(stage_addr + (uint32_t)(c >> 1) * EPI_BOX_BYTES, c & 1, lane, stats.best_val);
         }
       }
       if (STATS && row_ok) {
@@ -829,27 +908,48 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
 
 }  // namespace gemm
 
-// Row argmax (and optionally the row log-sum-exp) from the per-slice partials the GEMM epilogue wrote: one thread
-// per row walks the slices in column order; strict '>' keeps the lowest column among equal maxima.
-__global__ void __launch_bounds__(256)
+// Row argmax (and optionally the row log-sum-exp) from the per-slice partials the GEMM epilogue wrote.  A block
+// covers 32 rows with 8 threads per row: thread (x, y) walks slices y, y + 8, ... of row x (32 consecutive rows of
+// one slice are one 128-byte line), then the 8 partial results of a row are merged through shared memory.  Strict
+// '>' within a thread and the lower column on equal values across threads keep the lowest column among equal maxima.
+constexpr int kReduceRows = 32, kReduceSplit = 8;
+__global__ void __launch_bounds__(kReduceRows * kReduceSplit)
 argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx, const float* __restrict__ sum, int64_t ld, int slices,
                      int64_t M, int64_t* __restrict__ out, float* __restrict__ lse_out) {
-  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= M) return;
-  float best = -INFINITY;
-  int where = 0;
-  for (int s = 0; s < slices; ++s) {
-    const float v = val[(int64_t)s * ld + row];
-    if (v > best) best = v, where = idx[(int64_t)s * ld + row];
-  }
-  out[row] = where;
-  if (lse_out) {
-    float total = 0.f;
-    for (int s = 0; s < slices; ++s) {
+  __shared__ float s_val[kReduceSplit][kReduceRows];
+  __shared__ int s_idx[kReduceSplit][kReduceRows];
+  __shared__ float s_sum[kReduceSplit][kReduceRows];
+  const int x = threadIdx.x & (kReduceRows - 1), y = threadIdx.x / kReduceRows;
+  const int64_t row = (int64_t)blockIdx.x * kReduceRows + x;
+  float best = -INFINITY, total = 0.f;
+  int where = 0x7fffffff;
+  if (row < M) {
+    for (int s = y; s < slices; s += kReduceSplit) {
       const float v = val[(int64_t)s * ld + row];
-      if (v > -INFINITY) total += sum[(int64_t)s * ld + row] * expf(v - best);
+      if (v > best) {
+        if (sum) total *= __expf(best - v);  // re-base what was summed so far (0 * exp(-inf) = 0 the first time)
+        best = v, where = idx[(int64_t)s * ld + row];
+      }
+      if (sum && v > -INFINITY) total += sum[(int64_t)s * ld + row] * __expf(v - best);
     }
-    lse_out[row] = best + logf(total);
+  }
+  s_val[y][x] = best, s_idx[y][x] = where, s_sum[y][x] = total;
+  __syncthreads();
+  if (y == 0 && row < M) {
+#pragma unroll
+    for (int k = 1; k < kReduceSplit; ++k) {
+      const float v = s_val[k][x];
+      const int w = s_idx[k][x];
+      const float t = s_sum[k][x];
+      if (v > best || (v == best && w < where)) {
+        total = total * (best > -INFINITY ? __expf(best - v) : 0.f) + t;
+        best = v, where = w;
+      } else if (v > -INFINITY) {
+        total += t * __expf(v - best);
+      }
+    }
+    out[row] = where == 0x7fffffff ? 0 : where;
+    if (lse_out) lse_out[row] = best + logf(total);
   }
 }
 
@@ -905,7 +1005,7 @@ int launch_gemm_argmax(const void* a, const void* b, const void* bias, const voi
 #undef B200_GEMM_DISPATCH
   if (st != B200_OK || !argmax_out) return st;
   const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
-  argmax_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
+  argmax_reduce_kernel<<<(unsigned)((M + kReduceRows - 1) / kReduceRows), kReduceRows * kReduceSplit, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
   note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }
@@ -939,7 +1039,7 @@ int launch_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t
   else
     st = launch_typed<__nv_bfloat16, false, 3>(a, b, bias, nullptr, nullptr, M, N, K, lda, ldb, 0, N, op_dtype, am, status_word, stream, targets, target_out);
   if (st != B200_OK) return st;
-  argmax_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
+  argmax_reduce_kernel<<<(unsigned)((M + kReduceRows - 1) / kReduceRows), kReduceRows * kReduceSplit, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
   note_launches(1);
   return status_from_cuda(cudaGetLastError());
 }
