@@ -438,51 +438,71 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
   }
 }
 
-// Statistics-only epilogue (nothing is stored): the 32 values a thread would have written, rounded to the output
-// type as the storing epilogue rounds them, update the row's running maximum / column / sum of exponentials, and
-// the value at column `tgt` (if it falls into this chunk) is picked out.
+// Statistics-only epilogue (nothing goes to global memory): the 32 values a thread would have written, rounded to
+// the output type as the storing epilogue rounds them, update the row's running maximum / column and, if wanted,
+// its sum of exponentials; the value at column `tgt` (if it falls into this chunk) is picked out.
 template <typename OutT>
-__device__ __forceinline__ void stats_only_chunk(const uint32_t (&acc)[32], const float* bias_s, bool has_bias, int col0, int64_t N, int tgt,
-                                                 RowStats& st, float& picked) {
+__device__ __forceinline__ void stats_only_chunk(const uint32_t (&acc)[32], const float* bias_s, bool has_bias, bool want_lse, int col0, int64_t N,
+                                                 int tgt, uint32_t box, int half, int lane, RowStats& st, float& picked) {
+  static_assert(sizeof(OutT) == 2, "row statistics without the product are built for 16-bit rounding");
   float f[32];
   if (has_bias) {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
       const float4 b = *reinterpret_cast<const float4*>(bias_s + j);
-      f[j] = __uint_as_float(acc[j]) + b.x;
-      f[j + 1] = __uint_as_float(acc[j + 1]) + b.y;
-      f[j + 2] = __uint_as_float(acc[j + 2]) + b.z;
-      f[j + 3] = __uint_as_float(acc[j + 3]) + b.w;
+      const float2 lo = __fadd2_rn(make_float2(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1])), make_float2(b.x, b.y));
+      const float2 hi = __fadd2_rn(make_float2(__uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3])), make_float2(b.z, b.w));
+      f[j] = lo.x, f[j + 1] = lo.y, f[j + 2] = hi.x, f[j + 3] = hi.y;
     }
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(acc[j]);
   }
-  if constexpr (sizeof(OutT) == 2) {
+  uint32_t w[16];
 #pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-      const float2 r = unpack2<OutT>(pack2<OutT>(f[j], f[j + 1]));
-      f[j] = r.x, f[j + 1] = r.y;
-    }
-  }
+  for (int j = 0; j < 16; ++j) w[j] = pack2<OutT>(f[2 * j], f[2 * j + 1]);
   const float m_old = st.best_val;
   const bool full = col0 + 32 <= N;
+  if (full) {
+    // chunk maximum with packed 16-bit max instructions; the chunk is parked in the warp's staging tile so that the
+    // column of the tile's maximum can be looked up once per tile (find_staged_column)
+    const uint32_t rowaddr = box + (uint32_t)lane * 128u;
+    const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll
-  for (int j = 0; j < 32; ++j)
-    if ((full || col0 + j < N) && f[j] > st.best_val) st.best_val = f[j], st.best_idx = col0 + j, st.pending_col0 = -1;  // strict '>': lowest column wins ties
-  if (st.best_val > -INFINITY) {
+    for (int g = 0; g < 4; ++g) st_shared_v4(rowaddr + ((((uint32_t)(half * 4 + g)) ^ sw) << 4), w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+    uint32_t m = w[0];
+#pragma unroll
+    for (int j = 1; j < 16; ++j) m = max2<OutT>(m, w[j]);
+    const float2 mm = unpack2<OutT>(m);
+    const float cm = fmaxf(mm.x, mm.y);
+    if (cm > st.best_val) st.best_val = cm, st.pending_col0 = col0;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 r = unpack2<OutT>(w[j]);
+      if (col0 + 2 * j < N && r.x > st.best_val) st.best_val = r.x, st.best_idx = col0 + 2 * j, st.pending_col0 = -1;  // strict '>': lowest column wins ties
+      if (col0 + 2 * j + 1 < N && r.y > st.best_val) st.best_val = r.y, st.best_idx = col0 + 2 * j + 1, st.pending_col0 = -1;
+    }
+  }
+  if (want_lse && st.best_val > -INFINITY) {
     const float kLog2e = 1.4426950408889634f;
     const float m2 = st.best_val * kLog2e;
     float acc_sum = st.sumexp * ex2_approx(m_old * kLog2e - m2);
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (full || col0 + j < N) acc_sum += ex2_approx(fmaf(f[j], kLog2e, -m2));
+    for (int j = 0; j < 16; ++j) {
+      const float2 r = unpack2<OutT>(w[j]);
+      if (full || col0 + 2 * j < N) acc_sum += ex2_approx(fmaf(r.x, kLog2e, -m2));
+      if (full || col0 + 2 * j + 1 < N) acc_sum += ex2_approx(fmaf(r.y, kLog2e, -m2));
+    }
     st.sumexp = acc_sum;
   }
   if (tgt >= col0 && tgt < col0 + 32) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j == tgt) picked = f[j];
+    for (int j = 0; j < 16; ++j) {
+      const float2 r = unpack2<OutT>(w[j]);
+      if (col0 + 2 * j == tgt) picked = r.x;
+      if (col0 + 2 * j + 1 == tgt) picked = r.y;
+    }
   }
 }
 
@@ -650,6 +670,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const bool use_tma = STATS != 3 && esz == 2 && epi.tma_store != 0;
     const bool res_tma = use_tma && epi.residual != nullptr;  // (the host only sets tma_store when the residual can be mapped too)
     const uint32_t stage_addr = use_tma ? smem_epi + (uint32_t)(warp - 2) * EPI_WARP_STAGE_BYTES : 0u;
+    const uint32_t stats_stage = smem_epi + (uint32_t)(warp - 2) * EPI_WARP_STAGE_BYTES;  // statistics-only launches park chunks here
     const uint32_t my_res_bar = bar_res + 8 * (uint32_t)(warp - 2);
     uint32_t res_phase = 0;
     for (int64_t t = group_id; t < num_tiles; t += num_groups) {
@@ -707,7 +728,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tgt = (t64 >= col_base && t64 < col_base + EPI_COLS) ? (int)t64 : -1;
         }
       }
-#pragma unroll
+#pragma unroll(STATS == 2 ? 1 : EPI_CHUNKS)  // argmax + log-sum-exp + store: rolled, or the unrolled body spills
       for (int c = 0; c < EPI_CHUNKS; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
@@ -722,7 +743,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         const int col0 = col_base + c * 32;
         if constexpr (STATS == 3) {
-          if (row_ok && col0 < N) stats_only_chunk<OutT>(v, bias_s + col_half * EPI_COLS + c * 32, epi.bias != nullptr, col0, N, tgt, stats, picked);
+          if constexpr (sizeof(OutT) == 2) {
+            if (row_ok && col0 < N)
+              stats_only_chunk<OutT>(v, bias_s + col_half * EPI_COLS + c * 32, epi.bias != nullptr, epi.amax_sum != nullptr, col0, N, tgt,
+                                     stats_stage + (uint32_t)(c >> 1) * EPI_BOX_BYTES, c & 1, lane, stats, picked);
+          }
         } else if (use_tma) {
           const uint32_t box = stage_addr + (uint32_t)(c >> 1) * EPI_BOX_BYTES;
           if (!res_tma && (c & 1) == 0) {
@@ -747,19 +772,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                      0, lane, row_ok, false, stats);
         }
       }
-      if constexpr (STATS == 1 || STATS == 2) {
+      if constexpr (STATS != 0 && sizeof(OutT) == 2) {
         if (stats.pending_col0 >= 0) {
           // the winning chunk still sits in this warp's staging boxes (nothing overwrites them before the next tile)
           const int c = (stats.pending_col0 - col_base) >> 5;
-          stats.best_idx = stats.pending_col0 +
-                           find_staged_column<OutT>(stage_addr + (uint32_t)(c >> 1) * EPI_BOX_BYTES, c & 1, lane, stats.best_val);
+          stats.best_idx = stats.pending_col0 + find_staged_column<OutT>((STATS == 3 ? stats_stage : stage_addr) + (uint32_t)(c >> 1) * EPI_BOX_BYTES,
+                                                                         c & 1, lane, stats.best_val);
         }
       }
       if (STATS && row_ok) {
         const int64_t slice = (int64_t)tc.n * (BN / EPI_COLS) + col_half;
         epi.amax_val[slice * epi.amax_ld + row] = stats.best_val;
         epi.amax_idx[slice * epi.amax_ld + row] = stats.best_idx;
-        if (STATS >= 2) epi.amax_sum[slice * epi.amax_ld + row] = stats.sumexp;
+        if (STATS == 2 || (STATS == 3 && epi.amax_sum)) epi.amax_sum[slice * epi.amax_ld + row] = stats.sumexp;
         if (STATS == 3 && tgt >= 0 && tgt < N) epi.target_val[row] = picked;
       }
       if (++acc == 2) {
@@ -1016,7 +1041,7 @@ int launch_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t
                          int op_dtype, int round_dtype, const int64_t* targets, int64_t* argmax_out, float* lse_out, float* target_out,
                          void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream) {
   using namespace gemm;
-  if (!argmax_out || !lse_out || (targets != nullptr) != (target_out != nullptr)) return B200_ERR_BAD_ARGUMENT;
+  if (!argmax_out || (targets != nullptr) != (target_out != nullptr)) return B200_ERR_BAD_ARGUMENT;
   if (K < 1 || M < 0 || N < 0) return B200_ERR_BAD_ARGUMENT;
   if (M == 0 || N == 0) return B200_OK;
   if (op_dtype != B200_F16 && op_dtype != B200_BF16) return B200_ERR_BAD_ARGUMENT;
@@ -1032,7 +1057,7 @@ int launch_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t
   const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
   am.val = static_cast<float*>(workspace);
   am.idx = reinterpret_cast<int*>(am.val + slices * am.ld);
-  am.sum = am.val + 2 * slices * am.ld;
+  am.sum = lse_out ? am.val + 2 * slices * am.ld : nullptr;
   int st;
   if (round_dtype == B200_F16)
     st = launch_typed<__half, false, 3>(a, b, bias, nullptr, nullptr, M, N, K, lda, ldb, 0, N, op_dtype, am, status_word, stream, targets, target_out);

@@ -193,7 +193,8 @@ class FusedGPT(_EvalOnly):
         if hidden.dtype == torch.float32:
             return self.lm_head(hidden, return_argmax=True)[1]
         B, L, h = hidden.shape
-        return K.ffn_row_statistics(hidden.reshape(B * L, h), self._operand(self.wte_weight, weight_is_nk=True))[0].view(B, L)
+        w = self._operand(self.wte_weight, weight_is_nk=True)
+        return K.ffn_row_statistics(hidden.reshape(B * L, h), w, want_lse=False)[0].view(B, L)
 
     @torch.no_grad()
     def token_nll(self, x, targets):

@@ -223,13 +223,13 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
 
 
 @torch.no_grad()
-def ffn_row_statistics(x, weight, bias=None, targets=None):
+def ffn_row_statistics(x, weight, bias=None, targets=None, want_lse=True):
     """Row statistics of z = x @ weight (+ bias) without materialising z (no counterpart in the reference, whose
     lm_head is commented out, gpt.py:172-179): ``(ids, lse, target_value)`` with ids (*,) int64 the argmax of each
     row (lowest column on ties), lse (*,) float32 = log(sum_j exp(z[row, j])) and, when ``targets`` (*,) int64 is
     given, target_value (*,) float32 = z[row, targets[row]] (NaN where the target is outside [0, N); else None) --
-    all over z rounded to x.dtype exactly as fused_ffn would store it.  ``weight`` must be a PackedWeight, x 16-bit
-    with K % 8 == 0."""
+    all over z rounded to x.dtype exactly as fused_ffn would store it.  ``want_lse=False`` skips the log-sum-exp
+    (lse is None; one exponential per element less).  ``weight`` must be a PackedWeight, x 16-bit with K % 8 == 0."""
     assert isinstance(weight, PackedWeight), "ffn_row_statistics needs a PackedWeight"
     require_cuda(x, bias, targets)
     lead = x.shape[:-1]
@@ -243,7 +243,7 @@ def ffn_row_statistics(x, weight, bias=None, targets=None):
     if bias is not None:
         assert bias.is_contiguous() and bias.shape[0] == N and bias.dtype == x.dtype
     ids = torch.empty((M,), device=dev, dtype=torch.int64)
-    lse = torch.empty((M,), device=dev, dtype=torch.float32)
+    lse = torch.empty((M,), device=dev, dtype=torch.float32) if want_lse else None
     picked = None
     if targets is not None:
         targets = targets.reshape(-1)
@@ -254,10 +254,10 @@ def ffn_row_statistics(x, weight, bias=None, targets=None):
     ws = torch.empty((max(need, 16),), device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
         st = lib.b200_gemm_rowstats(x.data_ptr(), weight.data.data_ptr(), _ptr(bias), M, N, K, K, weight.data.stride(0),
-                                    dtype_code(weight.data.dtype), dt, _ptr(targets), ids.data_ptr(), lse.data_ptr(), _ptr(picked),
+                                    dtype_code(weight.data.dtype), dt, _ptr(targets), ids.data_ptr(), _ptr(lse), _ptr(picked),
                                     ws.data_ptr(), need, None, stream_ptr(dev))
     check(st, "ffn_row_statistics")
-    return ids.view(lead), lse.view(lead), (picked.view(lead) if picked is not None else None)
+    return ids.view(lead), (lse.view(lead) if want_lse else None), (picked.view(lead) if picked is not None else None)
 
 
 # ----------------------------------------------------------------------------- qkv split

@@ -105,7 +105,8 @@ int b200_gemm_argmax(const void* a, const void* b, const void* bias, const void*
 /*
  * Row statistics of the product without the product: for logits[M,N] = A[M,K] . B[N,K]^T (+ bias[N]) rounded to
  * round_dtype (F16 or BF16) exactly as b200_gemm would store them, returns per row argmax_out (int64, lowest column
- * on ties), lse_out (float, log-sum-exp over the rounded values) and, if `targets` (int64 [M], device) is not NULL,
+ * on ties), lse_out (float, log-sum-exp over the rounded values; may be NULL, which saves one exponential per
+ * logit) and, if `targets` (int64 [M], device) is not NULL,
  * target_logit_out[row] = logits[row, targets[row]] (float; rows whose target lies outside [0, N) are left
  * untouched).  Nothing of size M x N touches memory: the tied lm_head (gpt.py:159-161, 172-179 of the reference)
  * for greedy next-token ids or per-token cross-entropy (lse - target logit) without the [tokens, vocab] tensor.

@@ -263,6 +263,8 @@ def test_ffn_row_statistics_without_the_product(M, N, K_, use_bias, dtype):
     assert torch.isnan(picked.cpu()[~ok]).all()
     ids2, lse2, none = k.ffn_row_statistics(cu(x), pw, bias=cu(b))
     assert none is None and torch.equal(ids2, ids) and torch.equal(lse2, lse)
+    ids3, none_lse, _ = k.ffn_row_statistics(cu(x), pw, bias=cu(b), want_lse=False)
+    assert none_lse is None and torch.equal(ids3, ids)
     # leading dimensions are kept
     if M % 3 == 0:
         i3, l3, p3 = k.ffn_row_statistics(cu(x).view(3, M // 3, K_), pw, bias=cu(b), targets=cu(tgt).view(3, M // 3))
