@@ -53,6 +53,15 @@ def test_argument_checks_need_no_gpu():
     assert lib.b200_attention(None, None, None, None, 1, 1, 4, 24, strides, strides, strides, strides, 1.0, 0, 0, None) == 1
     assert lib.b200_gemm(None, None, None, None, None, 4, 4, 0, 8, 8, 4, 4, 1, 1, 0, None, None) == 1  # K = 0
     assert lib.b200_ffn(None, None, None, None, None, 0, 4, 4, 4, 0, 0, 1, None, 0, None, None) == 0  # M = 0
+    # row statistics without the product: argmax_out is mandatory, targets and target_logit_out come together,
+    # the rounding type is 16-bit, and the workspace is checked before any launch
+    assert lib.b200_gemm_argmax_workspace_bytes(100, 1000) == 8 * 128 * 12  # 4 tiles of 256 columns x 2 slices, rows padded to 64
+    one = ctypes.c_void_p(256)
+    assert lib.b200_gemm_rowstats(one, one, None, 4, 4, 8, 8, 8, 1, 1, None, None, None, None, None, 0, None, None) == 1
+    assert lib.b200_gemm_rowstats(one, one, None, 4, 4, 8, 8, 8, 1, 1, one, one, None, None, None, 0, None, None) == 1
+    assert lib.b200_gemm_rowstats(one, one, None, 4, 4, 8, 8, 8, 1, 0, None, one, None, None, None, 0, None, None) == 4  # fp32 rounding: unsupported
+    assert lib.b200_gemm_rowstats(one, one, None, 4, 4, 8, 8, 8, 1, 1, None, one, None, None, None, 0, None, None) == 5  # no workspace
+    assert lib.b200_gemm_rowstats(one, one, None, 0, 4, 8, 8, 8, 1, 1, None, one, None, None, None, 0, None, None) == 0  # M = 0
 
 
 def test_operators_refuse_cpu_tensors():
