@@ -328,7 +328,7 @@ def run_gpu_arm(args, rank, world, local_rank):
                          "peak_source": f"{peak_kind}: cuBLAS bf16 sustained",
                          # DRAM bytes of one c_fc launch (153600 x 3072 x 768): dram read+write of the ncu capture of a
                          # 32768-row launch (profiles/gemm_tn_kernel_bias_gelu_32768x3072x768_fp16.md) scaled by 153600/32768
-                         "traffic": (55.16e6 + 143.31e6) * 153600 / 32768, "traffic_algorithmic": 2.0 * (153600 * 768 + 768 * 3072 + 153600 * 3072),
+                         "traffic": (55.15e6 + 146.48e6) * 153600 / 32768, "traffic_algorithmic": 2.0 * (153600 * 768 + 768 * 3072 + 153600 * 3072),
                          "per_shape": detail},
             "cpu_baseline": cpu,
             "clocks": clocks,
