@@ -338,8 +338,9 @@ def run_gpu_arm(args, rank, world, local_rank):
 # ----------------------------------------------------------------------------- standalone kernel sweep
 def run_sweep(args):
     """Single-kernel timings at the kernel-sweep shapes (fp16, seed 0): GEMM + bias + GELU with
-    M=153600, K=768, N=3072; LayerNorm and embedding on 153600 x 768; causal attention with B=512,
-    H=12, D=64, S in {300, 1024, 2048}.  --rows / --batch shrink the problem (for profiler captures).
+    M=153600, K=768, N=3072; the tied lm_head (M=153600, K=768, N=50257: logits, logits + row argmax, row argmax
+    without logits); LayerNorm and embedding on 153600 x 768; causal attention with B=512, H=12, D=64,
+    S in {300, 1024, 2048}.  --rows / --batch shrink the problem (for profiler captures).
     One JSON line per kernel; not the headline metric."""
     from gpt_triton_b200 import kernels as K
 
@@ -380,6 +381,17 @@ def run_sweep(args):
         ms = timed(lambda: K.fused_ffn(x, pw, bias=b, add_gelu=True, out=out))
         report("gemm_bias_gelu", ms, "tensor", 2.0 * M * 768 * 3072, float(peaks["bf16_tflops"]), {"M": M, "K": 768, "N": 3072})
         del x, out
+    if which in ("lm_head", "all"):
+        x = torch.randn((M, 768), generator=g).half().to(dev)
+        wte = (torch.randn((50257, 768), generator=g) * 0.02).half().to(dev)
+        pw = K.pack_weight(wte, weight_is_nk=True)
+        pitch = (50257 + 63) // 64 * 64
+        buf = torch.empty((M, pitch), device=dev, dtype=torch.float16)
+        for name, fn in (("lm_head_logits", lambda: K.fused_ffn(x, pw, out=buf[:, :50257])),
+                         ("lm_head_logits_argmax", lambda: K.fused_ffn(x, pw, out=buf[:, :50257], return_argmax=True)),
+                         ("lm_head_argmax_only", lambda: K.ffn_row_statistics(x, pw, want_lse=False))):
+            report(name, timed(fn), "tensor", 2.0 * M * 768 * 50257, float(peaks["bf16_tflops"]), {"M": M, "K": 768, "N": 50257})
+        del x, buf, wte, pw
     if which in ("layernorm", "all"):
         x = torch.randn((M, 768), generator=g).half().to(dev)
         w, b = torch.ones(768, device=dev).half(), torch.zeros(768, device=dev).half()
@@ -445,7 +457,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--sweep", default=None, choices=["gemm", "layernorm", "embedding", "attention", "all"],
+    ap.add_argument("--sweep", default=None, choices=["gemm", "lm_head", "layernorm", "embedding", "attention", "all"],
                     help="time single kernels at the kernel-sweep shapes instead of the forward")
     ap.add_argument("--rows", type=int, default=0, help="--sweep: rows (tokens) instead of 153600")
     ap.add_argument("--batch", type=int, default=0, help="--sweep attention: batch instead of 512")

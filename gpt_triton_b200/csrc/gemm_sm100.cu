@@ -84,18 +84,25 @@ __host__ __device__ constexpr uint32_t make_idesc(int ab_format, int mma_m) {
 struct TileCoord {
   int m, n;
 };
-// Raster: groups of GROUP_M row tiles (GROUP_ROWS rows); inside a group the row tile varies fastest, so the CTAs
-// that run at the same time share a few B column tiles and GROUP_M A row tiles in L2.
+// Raster: the column tiles are cut into panels of panel_n tiles (the host sizes a panel so that its part of B stays
+// in L2: with a vocabulary-sized N the whole of B does not, and would be fetched from HBM again for every row
+// group); inside a panel, groups of GROUP_M row tiles (GROUP_ROWS rows); inside a group the row tile varies
+// fastest, so the CTAs that run at the same time share a few B column tiles and GROUP_M A row tiles in L2.
 template <int GROUP_M>
-__device__ __forceinline__ TileCoord tile_coord(int64_t t, int m_tiles, int n_tiles) {
-  const int64_t per_group = (int64_t)GROUP_M * n_tiles;
-  const int group = (int)(t / per_group);
-  const int within = (int)(t - (int64_t)group * per_group);
+__device__ __forceinline__ TileCoord tile_coord(int64_t t, int m_tiles, int n_tiles, int panel_n) {
+  const int64_t per_panel = (int64_t)m_tiles * panel_n;
+  const int panel = (int)(t / per_panel);
+  const int64_t rem = t - (int64_t)panel * per_panel;
+  const int n_first = panel * panel_n;
+  const int pn = min(panel_n, n_tiles - n_first);
+  const int64_t per_group = (int64_t)GROUP_M * pn;
+  const int group = (int)(rem / per_group);
+  const int within = (int)(rem - (int64_t)group * per_group);
   const int m_first = group * GROUP_M;
   const int gm = min(GROUP_M, m_tiles - m_first);
   TileCoord c;
   c.m = m_first + within % gm;
-  c.n = within / gm;
+  c.n = n_first + within / gm;
   return c;
 }
 
@@ -130,6 +137,9 @@ struct EpilogueArgs {
   // Statistics-only launches: optional per-row target column and where that row's (rounded) value at it goes.
   const int64_t* targets;
   float* target_val;
+  // Output is written once and not read back soon, and B is large: store it with evict-first priority so that it
+  // does not push B out of L2 (the tied lm_head: 77 MB of B against gigabytes of logits).
+  int stream_out;
 };
 
 // x * sigmoid(2y), y = sqrt(2/pi) (x + 0.044715 x^3): algebraically the reference's
@@ -175,6 +185,17 @@ __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&v)[8]) {
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1)
                : "memory");
+}
+// The same store with an L2 eviction-priority hint (a policy word from createpolicy).
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, uint32_t src, int c0, int c1, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(map), "r"(src),
+               "r"(c0), "r"(c1), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all of this thread's earlier bulk stores have finished READING shared memory
@@ -510,7 +531,7 @@ template <typename OutT, bool GELU, int CTAS, int STATS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res, EpilogueArgs<OutT> epi,
-               int64_t M, int64_t N, int64_t K, uint32_t idesc, int* status_word) {
+               int64_t M, int64_t N, int64_t K, uint32_t idesc, int panel_n, int* status_word) {
   using C = Cfg<CTAS>;
   constexpr int STAGES = C::STAGES;
   // 128-byte-swizzled tiles need 1024-byte aligned bases (the dynamic shared memory base is the same in both
@@ -588,7 +609,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // completion bytes of both CTAs' loads are posted on the leader's full barrier
       const uint32_t full_base = CTAS == 2 ? mapa_shared(bar_full, 0) : bar_full;
       for (int64_t t = group_id; t < num_tiles && alive; t += num_groups) {
-        const TileCoord tc = tile_coord<C::GROUP_M>(t, m_tiles, n_tiles);
+        const TileCoord tc = tile_coord<C::GROUP_M>(t, m_tiles, n_tiles, panel_n);
         const int row_a = tc.m * C::TILE_M + (int)cta_rank * BM;
         const int row_b = tc.n * BN + (int)cta_rank * C::B_ROWS;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -673,8 +694,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t stats_stage = smem_epi + (uint32_t)(warp - 2) * EPI_WARP_STAGE_BYTES;  // statistics-only launches park chunks here
     const uint32_t my_res_bar = bar_res + 8 * (uint32_t)(warp - 2);
     uint32_t res_phase = 0;
+    const uint64_t out_policy = l2_policy_evict_first();
     for (int64_t t = group_id; t < num_tiles; t += num_groups) {
-      const TileCoord tc = tile_coord<C::GROUP_M>(t, m_tiles, n_tiles);
+      const TileCoord tc = tile_coord<C::GROUP_M>(t, m_tiles, n_tiles, panel_n);
       const int64_t row = (int64_t)tc.m * C::TILE_M + (int64_t)cta_rank * BM + quarter * 32 + lane;
       const int col_base = tc.n * BN + col_half * EPI_COLS;
       const int row_warp = (int)(tc.m * C::TILE_M + (int)cta_rank * BM + quarter * 32);  // first row of this warp's 32
@@ -763,7 +785,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             const int box_col = col_base + (c >> 1) * EPI_BOX_COLS;
             if (lane == 0) {
-              if (box_col < N && row_warp < M) tma_store_2d(&map_out, box, box_col, row_warp);
+              if (box_col < N && row_warp < M) {
+                if (epi.stream_out) tma_store_2d_hint(&map_out, box, box_col, row_warp, out_policy);
+                else tma_store_2d(&map_out, box, box_col, row_warp);
+              }
               tma_store_commit();  // always one bulk group per box and tile (possibly empty): the waits above count groups
             }
           }
@@ -894,7 +919,10 @@ static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CU
   attr.val.clusterDim.x = CTAS, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tn_kernel<OutT, GELU, CTAS, STATS>, ma, mb, mo, mr, epi, M, N, K, idesc, status_word);
+  // column panel: about 16 MB of B (panel_n * 256 rows of K 16-bit elements), at least 8 tiles
+  int panel_n = (int)(16e6 / ((double)BN * (double)K * 2.0));
+  if (panel_n < 8) panel_n = 8;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tn_kernel<OutT, GELU, CTAS, STATS>, ma, mb, mo, mr, epi, M, N, K, idesc, panel_n, status_word);
   note_launches(1);
   return status_from_cuda(e);
 }
@@ -903,7 +931,7 @@ template <typename OutT, bool GELU, int STATS>
 static int launch_typed(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K,
                         int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, const ArgmaxPartials& am, int* status_word,
                         cudaStream_t stream, const int64_t* targets = nullptr, float* target_val = nullptr) {
-  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.sum, am.ld, targets, target_val};
+  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.sum, am.ld, targets, target_val, 0};
   CUtensorMap mo, mr;
   memset(&mo, 0, sizeof(mo));
   memset(&mr, 0, sizeof(mr));
@@ -913,6 +941,7 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
       make_out_map(&mo, out, M, N, ld_out, DType<OutT>::code) == B200_OK &&
       (!residual || make_out_map(&mr, const_cast<void*>(residual), M, N, ld_res, DType<OutT>::code) == B200_OK))
     epi.tma_store = 1;
+  epi.stream_out = epi.tma_store && (double)N * (double)K * 2.0 >= 32e6 && (double)M * (double)N * sizeof(OutT) >= 512e6;
   const int64_t n_tiles = (N + BN - 1) / BN;
   const int pairs = M > BM ? max_pairs<OutT, GELU, STATS>() : 0;
   CUtensorMap ma, mb;
