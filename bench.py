@@ -59,13 +59,17 @@ def make_ids(batch, seed):
 
 # ----------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi.  It is started before the warm-up passes
+    (nvidia-smi needs a second or more to come up on a multi-GPU box) and keeps only the samples that arrived
+    between mark_begin() and mark_end(), the timed region; if the region was too short to catch one, the samples of
+    the warm-up passes (same kernels, same load) stand in and the record says so."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.rows, self.proc, self.thread = [], None, None
+        self.t_begin = self.t_end = None
         self.cmd = ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"]
 
     def start(self):
@@ -73,30 +77,48 @@ class ClockSampler:
             self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
-        self.thread = threading.Thread(target=lambda: self.rows.extend(self.proc.stdout), daemon=True)
+
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append((time.monotonic(), line))
+
+        self.thread = threading.Thread(target=pump, daemon=True)
         self.thread.start()
+
+    def mark_begin(self):
+        self.t_begin = time.monotonic()
+
+    def mark_end(self):
+        self.t_end = time.monotonic()
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.12)  # one more sampling period: a sample describes the 100 ms before it
         self.proc.terminate()
         self.thread.join(timeout=5)
+        inside = [line for t, line in self.rows if self.t_begin is not None and self.t_begin <= t <= (self.t_end or t) + 0.12]
+        window = "timed region"
+        if not inside:
+            inside = [line for _, line in self.rows]
+            window = "warm-up passes and timed region (the timed region was shorter than one sampling period)"
         sm, mx, reasons = [], [], set()
-        for line in self.rows:
+        for line in inside:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                clock, top = float(parts[0]), float(parts[1])
             except ValueError:
                 continue
+            sm.append(clock)
+            mx.append(top)
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[4:8]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        busy = [s for s in sm if s > 0]
+        busy = [c for c in sm if c > 0]
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(busy)}
+                "reasons": sorted(reasons), "samples": len(busy), "window": window}
 
 
 # ----------------------------------------------------------------------------- CPU arm
@@ -175,23 +197,27 @@ def run_gpu_arm(args, rank, world, local_rank):
     # GraphedForward) and replayed, so that host-side launch jitter on a shared box cannot starve the GPU
     from gpt_triton_b200.gpt import GraphedForward
 
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    if rank == 0:
+        sampler.start()  # only rank 0's GPU is reported; eight nvidia-smi processes at once slow each other down
     for _ in range(args.warmup):
         model.logits(ids_dev)
     launches_before_capture = lib.b200_launch_count()
     fwd = GraphedForward(model, ids_dev, what="logits", warmup=1)
     torch.cuda.synchronize()
     launches_per_forward = (lib.b200_launch_count() - launches_before_capture) // 2  # one warm-up pass + the captured pass
-    fwd.graph.replay()
-    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    for _ in range(max(1, args.warmup)):
+        fwd.graph.replay()
     barrier()
-    sampler.start()
+    sampler.mark_begin()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
         fwd.graph.replay()
     end.record()
     barrier()
-    clocks = sampler.stop()
+    sampler.mark_end()
+    clocks = sampler.stop() if rank == 0 else None
     launches = launches_per_forward * args.steps
     ms_total = max_over_ranks(start.elapsed_time(end))
     ms_per_step = ms_total / args.steps
