@@ -127,6 +127,12 @@ def cpu_forward_tokens_per_s(steps, warmup):
     on CPU_SAMPLE_BATCH x 300 tokens of the benchmark batch per step."""
     from oracle import gpt2_oracle as orc
 
+    # every host core this process may use: torchrun exports OMP_NUM_THREADS=1 to its workers, which would leave the
+    # CPU arm on a single thread
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     cfg, sd = make_state_dict(torch.float16)
     ids = make_ids(BATCH, 0)[:CPU_SAMPLE_BATCH]
     times = []
