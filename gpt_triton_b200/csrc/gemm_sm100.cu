@@ -21,6 +21,13 @@
 // Two 128x256 accumulators (2 x 256 columns) let the epilogue of tile i overlap the main
 // loop of tile i+1.  Every wait on an mbarrier is bounded; a wait that gives up raises a
 // CTA-wide abort flag, reports through status_word and the kernel drains and exits.
+//
+// Optional row statistics (template parameter STATS) for the tied lm_head: 1 = row argmax next to the stored
+// product, 2 = argmax and log-sum-exp, 3 = argmax, optional log-sum-exp and the value at a per-row target column
+// with nothing stored.  On a power-capped part every epilogue instruction per output element shows up in the
+// clock of the main loop, so the epilogue is kept lean: packed fp32x2 adds/multiplies, no add without a bias,
+// the row maximum by packed 16-bit max instructions over the rounded values with one column look-up per tile
+// in the staging boxes, per-slice partials reduced by a small second kernel.
 #include <string.h>
 
 #include <atomic>
