@@ -1,0 +1,52 @@
+"""The benchmark's output contract: one JSON line with the agreed keys, for the CPU reference arm (runs anywhere)
+and for the GPU arm (needs a B200)."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+from conftest import ROOT
+
+BENCH = os.path.join(ROOT, "bench.py")
+COMMON = ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline",
+          "dtype", "data", "config", "e2e", "gpu_launches", "cpu_baseline")
+
+
+def run_bench(*flags):
+    res = subprocess.run([sys.executable, BENCH, *flags], capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [line for line in res.stdout.splitlines() if line.strip()]
+    assert len(lines) == 1, "exactly one JSON line on stdout"
+    return json.loads(lines[0])
+
+
+def test_reference_arm_prints_the_contract_line():
+    d = run_bench("--impl", "reference", "--steps", "1", "--warmup", "0")
+    for key in COMMON:
+        assert key in d, key
+    assert d["impl"] == "reference" and d["metric"] == "gpt2_124m_fwd_tokens_per_s" and d["unit"] == "tokens/s"
+    assert d["value"] > 0 and d["higher_is_better"] is True and d["vs_baseline"] is None
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["value"] == d["value"]
+    assert d["e2e"] == {"value": d["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in d["config"]
+
+
+@pytest.mark.gpu
+def test_gpu_arm_prints_the_contract_line():
+    d = run_bench("--steps", "2", "--warmup", "3", "--skip-cpu-baseline")
+    for key in COMMON + ("roofline", "clocks"):
+        assert key in d, key
+    assert d["n_gpus"] == 1 and d["steps"] == 2 and d["warmup"] == 3 and d["scaling"] == "weak" and d["dtype"] == "fp16"
+    assert d["value"] > 1e6 and abs(d["value"] - 512 * 300 / (d["ms_per_step"] * 1e-3)) < 1.0
+    assert d["gpu_launches"] == 87 * 2  # library kernels inside the timed region
+    e2e = d["e2e"]
+    assert e2e["h2d_bytes_per_step"] == 512 * 300 * 8 and e2e["d2h_bytes_per_step"] == 512 * 300 * 8
+    assert 0 < e2e["value"] and e2e["value"] != d["value"]
+    r = d["roofline"]
+    assert r["bound"] == "tensor" and r["unit"] == "TFLOP/s" and abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9
+    assert 0.3 < r["frac"] < 1.2 and r["traffic"] > 0
+    assert set(d["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
+    assert "workload" in d["config"] and "l2" in d["config"]
