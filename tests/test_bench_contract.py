@@ -34,6 +34,20 @@ def test_reference_arm_prints_the_contract_line():
     assert "workload" in d["config"]
 
 
+def test_reference_arm_under_torchrun_prints_once():
+    """Launched as two ranks (the way the multi-GPU arm is launched), rank 0 alone runs the CPU arm and prints; the
+    other rank exits 0 without output.  torchrun sets OMP_NUM_THREADS=1: the arm must still use the host's cores."""
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                          "--master-port", "29577", BENCH, "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [line for line in res.stdout.splitlines() if line.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["n_gpus"] == 2
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+
+
 @pytest.mark.gpu
 def test_gpu_arm_prints_the_contract_line():
     d = run_bench("--steps", "2", "--warmup", "3", "--skip-cpu-baseline")
