@@ -189,10 +189,11 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
             lse = torch.empty((M,), device=dev, dtype=torch.float32) if return_lse else None
             need = lib.b200_gemm_argmax_workspace_bytes(M, N)
             ws = torch.empty((max(need, 16),), device=dev, dtype=torch.uint8)
-            st = lib.b200_gemm_argmax(x.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, K,
-                                      packed.data.stride(0), N, ld_out, dtype_code(packed.data.dtype), dt, int(bool(add_gelu)),
-                                      ids.data_ptr(), _ptr(lse), ws.data_ptr(), need, None, stream)
-            check(st, "fused_ffn(argmax)")
+            if M > 0:  # (an empty tensor has a null data pointer, which the entry point takes for "not requested")
+                st = lib.b200_gemm_argmax(x.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, K,
+                                          packed.data.stride(0), N, ld_out, dtype_code(packed.data.dtype), dt, int(bool(add_gelu)),
+                                          ids.data_ptr(), _ptr(lse), ws.data_ptr(), need, None, stream)
+                check(st, "fused_ffn(argmax)")
             zz = z if out is not None else z.view((*out_shape_0, N))
             return (zz, ids.view(out_shape_0), lse.view(out_shape_0)) if return_lse else (zz, ids.view(out_shape_0))
         if packed is not None and dt != _lib.F32 and K % 8 == 0 and x.data_ptr() % 16 == 0:
@@ -249,6 +250,8 @@ def ffn_row_statistics(x, weight, bias=None, targets=None, want_lse=True):
         targets = targets.reshape(-1)
         assert targets.dtype == torch.int64 and targets.is_contiguous() and targets.shape[0] == M
         picked = torch.full((M,), float("nan"), device=dev, dtype=torch.float32)
+    if M == 0:
+        return ids.view(lead), (lse.view(lead) if want_lse else None), (picked.view(lead) if picked is not None else None)
     lib = _lib.load()
     need = lib.b200_gemm_argmax_workspace_bytes(M, N)
     ws = torch.empty((max(need, 16),), device=dev, dtype=torch.uint8)

@@ -412,6 +412,12 @@ def test_empty_inputs_are_no_ops():
     assert k.fused_ffn(torch.zeros((0, 64), device=DEV), torch.rand(64, 32, device=DEV)).shape == (0, 32)
     q = torch.zeros((0, 2, 7, 64), device=DEV, dtype=torch.float16)
     assert k.flash_attention_v1(q, q, q).shape == (0, 2, 7, 64)
+    pw = k.pack_weight(torch.rand(64, 32, device=DEV).half())
+    ids, lse, picked = k.ffn_row_statistics(torch.zeros((0, 64), device=DEV, dtype=torch.float16), pw,
+                                            targets=torch.zeros((0,), dtype=torch.long, device=DEV))
+    assert ids.shape == (0,) and lse.shape == (0,) and picked.shape == (0,)
+    z, ids = k.fused_ffn(torch.zeros((0, 64), device=DEV, dtype=torch.float16), pw, return_argmax=True)
+    assert z.shape == (0, 32) and ids.shape == (0,)
     torch.cuda.synchronize()
 
 
