@@ -146,6 +146,42 @@ def cpu_forward_tokens_per_s(steps, warmup):
     return ids.numel() / mean, mean, torch.get_num_threads()
 
 
+def cpu_hf_forward_tokens_per_s(steps, warmup):
+    """transformers' GPT2Model built from a config (no download) with the benchmark's weights, fp32, plus hidden @ wte.T:
+    the plain PyTorch forward the reference compares itself with (bench.py:26-52 of the reference), on the same
+    CPU_SAMPLE_BATCH x 300 tokens and host threads as the oracle arm.  None when transformers is not importable."""
+    try:
+        from transformers import GPT2Config, GPT2Model
+    except Exception:
+        return None
+    kw = GPT2_SMALL
+    hf_cfg = GPT2Config(vocab_size=kw["vocab_size"], n_positions=kw["block_size"], n_embd=kw["n_embd"], n_layer=kw["n_layer"],
+                        n_head=kw["n_head"], resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    hf = GPT2Model(hf_cfg).eval()
+    _, sd = make_state_dict(torch.float32)
+    top = {"wte.weight": "wte_weight", "wpe.weight": "wpe_weight", "ln_f.weight": "layer_norm_weight", "ln_f.bias": "layer_norm_bias"}
+    blk = [("ln_1", 0, "layer_norm"), ("attn.c_attn", 0, "c_attn"), ("attn.c_proj", 0, "c_proj"), ("ln_2", 1, "layer_norm"),
+           ("mlp.c_fc", 1, "ffn1"), ("mlp.c_proj", 1, "ffn2")]
+    hf_sd = {k: sd[v] for k, v in top.items()}
+    for i in range(kw["n_layer"]):
+        for stem, slot, ours in blk:
+            for kind in ("weight", "bias"):
+                hf_sd[f"h.{i}.{stem}.{kind}"] = sd[f"blocks.{i}.{slot}.{ours}_{kind}"]
+    missing, unexpected = hf.load_state_dict(hf_sd, strict=False)
+    assert not unexpected and all(".attn.bias" in m or ".attn.masked_bias" in m for m in missing), (missing, unexpected)
+    ids = make_ids(BATCH, 0)[:CPU_SAMPLE_BATCH]
+    times = []
+    with torch.no_grad():
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            logits = hf(ids).last_hidden_state @ hf.wte.weight.T
+            _ = logits.argmax(-1)
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+    mean = sum(times) / len(times)
+    return ids.numel() / mean, mean, torch.get_num_threads()
+
+
 def run_reference_arm(args, rank):
     if rank != 0:
         return
@@ -337,6 +373,10 @@ def run_gpu_arm(args, rank, world, local_rank):
         tps, mean_s, threads = cpu_forward_tokens_per_s(steps=2, warmup=1)
         cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
                "sample": f"{CPU_SAMPLE_BATCH} x {SEQ} tokens of the batch, 2 timed passes after 1 warm-up ({mean_s:.2f} s each)"}
+        hf = cpu_hf_forward_tokens_per_s(steps=1, warmup=1)
+        if hf is not None:
+            cpu["hf_gpt2_fp32"] = {"value": hf[0], "unit": "tokens/s", "cores": hf[2],
+                                   "what": "transformers GPT2Model (same weights, fp32) + hidden @ wte.T on the same sample"}
 
     if rank == 0:
         print(json.dumps({
