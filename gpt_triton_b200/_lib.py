@@ -33,7 +33,8 @@ SIGNATURES = {
     "b200_ffn_workspace_bytes": (c_size_t, [c_i64, c_i64, c_i64, c_int, c_int]),
     "b200_ffn": (c_int, [c_void_p] * 5 + [c_i64] * 4 + [c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "b200_ffn_static_scratch": (c_int, [c_void_p] * 5 + [c_i64] * 4 + [c_int, c_int, c_int, c_void_p, c_void_p]),
-    "b200_attention": (c_int, [c_void_p] * 4 + [c_i64] * 4 + [_p_i64] * 4 + [c_float, c_int, c_int, c_void_p]),
+    "b200_attention": (c_int, [c_void_p] * 4 + [c_i64] * 4 + [_p_i64] * 4 + [c_float, c_int, c_int, c_void_p, c_void_p]),
+    "b200_selftest_bounded_wait": (c_int, [c_void_p, c_i64, c_void_p]),
 }
 
 _lib = None

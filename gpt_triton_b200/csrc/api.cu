@@ -33,7 +33,7 @@ const char* b200_status_string(int status) {
 
 const char* b200_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
 
-int b200_abi_version(void) { return 3; }
+int b200_abi_version(void) { return 4; }
 
 uint64_t b200_launch_count(void) { return b200::launches_so_far(); }
 
@@ -136,13 +136,18 @@ int b200_ffn(const void* x, const void* w, const void* bias, const void* residua
 
 int b200_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L, int64_t D,
                    const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
-                   const int64_t o_strides[3], float scale, int in_dtype, int out_dtype, void* stream) {
+                   const int64_t o_strides[3], float scale, int in_dtype, int out_dtype, int* status_word, void* stream) {
   if (B < 0 || NH < 0 || L < 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return B200_ERR_BAD_ARGUMENT;
   if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256) return B200_ERR_BAD_ARGUMENT;
   if (B == 0 || NH == 0 || L == 0) return B200_OK;
   if (!q || !k || !v || !out || !q_strides || !k_strides || !v_strides || !o_strides) return B200_ERR_BAD_ARGUMENT;
   return note(b200::launch_attention(q, k, v, out, B, NH, L, D, q_strides, k_strides, v_strides, o_strides, scale, in_dtype,
-                                     out_dtype, (cudaStream_t)stream));
+                                     out_dtype, status_word, (cudaStream_t)stream));
+}
+
+int b200_selftest_bounded_wait(int* status_word, int64_t limit_cycles, void* stream) {
+  if (!status_word || limit_cycles < 1 || limit_cycles > 4000000000LL) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_bounded_wait_selftest(status_word, limit_cycles, (cudaStream_t)stream));
 }
 
 }  // extern "C"

@@ -318,13 +318,13 @@ static int dispatch_d(int64_t D, const void* q, const void* k, const void* v, vo
 
 int launch_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L,
                      int64_t D, const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, float scale,
-                     int in_dtype, int out_dtype, cudaStream_t stream) {
+                     int in_dtype, int out_dtype, int* status_word, cudaStream_t stream) {
   using namespace attn;
   if (B == 0 || NH == 0 || L == 0) return B200_OK;
   if (L > 0x7fffffffLL - BLOCK) return B200_ERR_BAD_ARGUMENT;
   {
     // tensor-core path for the shapes it covers; everything else takes the generic kernel below
-    const int st = launch_attention_sm100(q, k, v, out, B, NH, L, D, qs, ks, vs, os, scale, in_dtype, out_dtype, nullptr, stream);
+    const int st = launch_attention_sm100(q, k, v, out, B, NH, L, D, qs, ks, vs, os, scale, in_dtype, out_dtype, status_word, stream);
     if (st != B200_ERR_UNSUPPORTED) return st;
   }
   Strides sq{qs[0], qs[1], qs[2]}, sk{ks[0], ks[1], ks[2]}, sv{vs[0], vs[1], vs[2]}, so{os[0], os[1], os[2]};

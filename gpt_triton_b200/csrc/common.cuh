@@ -153,8 +153,10 @@ int launch_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t
                          void* workspace, size_t workspace_bytes, int* status_word, cudaStream_t stream);
 int launch_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L,
                      int64_t D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
-                     const int64_t* o_strides, float scale, int in_dtype, int out_dtype, cudaStream_t stream);
+                     const int64_t* o_strides, float scale, int in_dtype, int out_dtype, int* status_word, cudaStream_t stream);
 
+// One warp waiting (bounded) on a barrier that nothing completes: reports B200_ERR_DEVICE_WAIT through status_word.
+int launch_bounded_wait_selftest(int* status_word, int64_t limit_cycles, cudaStream_t stream);
 // tcgen05/TMA attention (head size 64, fp16); B200_ERR_UNSUPPORTED means "use the generic kernel".
 int launch_attention_sm100(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L, int64_t D,
                            const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,

@@ -36,13 +36,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one timed out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word, int where) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word, int where,
+                                          long long limit_cycles = WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1;
       if (status_word) atomicCAS(status_word, 0, where);
       return false;

@@ -39,6 +39,45 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+_status_words = {}
+
+
+def _status_ptr(dev):
+    """Address of the device int32 (one per GPU, allocated at first use) into which the tensor-core kernels report
+    when one of them abandons a bounded wait; None while a CUDA graph is being captured before the word exists."""
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    word = _status_words.get(idx)
+    if word is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = word
+    return word.data_ptr()
+
+
+def device_status(device=None, reset=True):
+    """0, or the code left by the first kernel on `device` that gave up a bounded on-chip wait since the last reset
+    (its results are then invalid).  Synchronises the device."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    word = _status_words.get(idx)
+    if word is None:
+        return 0
+    code = int(word.item())
+    if code and reset:
+        word.zero_()
+    return code
+
+
+def bounded_wait_selftest(limit_cycles=200_000_000, device=None):
+    """Launch the library's self-test (one warp waiting on a barrier that nothing completes) and return the status
+    code it reports once the wait has run out: B200_ERR_DEVICE_WAIT (6) on a healthy GPU.  Synchronises."""
+    dev = torch.device("cuda", torch.cuda.current_device() if device is None else torch.device(device).index)
+    word = torch.zeros(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.load().b200_selftest_bounded_wait(word.data_ptr(), int(limit_cycles), stream_ptr(dev)), "bounded_wait_selftest")
+    return int(word.item())
+
+
 def _same_device(*tensors):
     """Operands must live on one CUDA device; make it current so the launch lands there."""
     ts = [t for t in tensors if t is not None]
@@ -192,7 +231,7 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
             if M > 0:  # (an empty tensor has a null data pointer, which the entry point takes for "not requested")
                 st = lib.b200_gemm_argmax(x.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, K,
                                           packed.data.stride(0), N, ld_out, dtype_code(packed.data.dtype), dt, int(bool(add_gelu)),
-                                          ids.data_ptr(), _ptr(lse), ws.data_ptr(), need, None, stream)
+                                          ids.data_ptr(), _ptr(lse), ws.data_ptr(), need, _status_ptr(dev), stream)
                 check(st, "fused_ffn(argmax)")
             zz = z if out is not None else z.view((*out_shape_0, N))
             return (zz, ids.view(out_shape_0), lse.view(out_shape_0)) if return_lse else (zz, ids.view(out_shape_0))
@@ -200,7 +239,7 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
             # operands usable in place: straight to the tensor-core kernel
             st = lib.b200_gemm(x.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, K,
                                packed.data.stride(0), N, ld_out, dtype_code(packed.data.dtype), dt, int(bool(add_gelu)),
-                               None, stream)
+                               _status_ptr(dev), stream)
         elif packed is not None:
             # fp32 storage or ragged K: x still has to be rounded/padded into scratch
             kp = packed.data.stride(0)
@@ -208,7 +247,7 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
             st = lib.b200_pack_operand(x.data_ptr(), xs.data_ptr(), M, K, K, kp, 0, dt, dtype_code(xs.dtype), stream)
             check(st, "fused_ffn(pack x)")
             st = lib.b200_gemm(xs.data_ptr(), packed.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, kp,
-                               kp, N, ld_out, dtype_code(xs.dtype), dt, int(bool(add_gelu)), None, stream)
+                               kp, N, ld_out, dtype_code(xs.dtype), dt, int(bool(add_gelu)), _status_ptr(dev), stream)
         else:
             need = lib.b200_ffn_workspace_bytes(M, N, K, int(weight_is_nk), dt)
             # an unaligned x or weight view needs its operand packed too; ask for the worst case then
@@ -216,7 +255,7 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
                 need = lib.b200_ffn_workspace_bytes(M, N, K, 0, _lib.F32)
             ws = torch.empty((need,), device=dev, dtype=torch.uint8) if need else None
             st = lib.b200_ffn(x.data_ptr(), weight.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, ld_out,
-                              int(weight_is_nk), int(bool(add_gelu)), dt, _ptr(ws), need, None, stream)
+                              int(weight_is_nk), int(bool(add_gelu)), dt, _ptr(ws), need, _status_ptr(dev), stream)
     check(st, "fused_ffn")
     if out is not None:
         return z
@@ -258,7 +297,7 @@ def ffn_row_statistics(x, weight, bias=None, targets=None, want_lse=True):
     with torch.cuda.device(dev):
         st = lib.b200_gemm_rowstats(x.data_ptr(), weight.data.data_ptr(), _ptr(bias), M, N, K, K, weight.data.stride(0),
                                     dtype_code(weight.data.dtype), dt, _ptr(targets), ids.data_ptr(), _ptr(lse), _ptr(picked),
-                                    ws.data_ptr(), need, None, stream_ptr(dev))
+                                    ws.data_ptr(), need, _status_ptr(dev), stream_ptr(dev))
     check(st, "ffn_row_statistics")
     return ids.view(lead), (lse.view(lead) if want_lse else None), (picked.view(lead) if picked is not None else None)
 
@@ -317,6 +356,6 @@ def flash_attention_v1(q, k, v, dropout_prob=0.0, *, merged_heads=False):
     with torch.cuda.device(dev):
         st = _lib.load().b200_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), z.data_ptr(), B, N, Lq, H, _bhl_strides(q),
                                         _bhl_strides(k), _bhl_strides(v), _bhl_strides(zv), scale, dtype_code(q.dtype),
-                                        dtype_code(z.dtype), stream_ptr(dev))
+                                        dtype_code(z.dtype), _status_ptr(dev), stream_ptr(dev))
     check(st, "flash_attention_v1")
     return z.view(B, Lq, N * H) if merged_heads else z

@@ -35,7 +35,7 @@ enum {
 const char* b200_status_string(int status);
 /* cudaGetErrorString of the last failing CUDA call made by this library on this thread. */
 const char* b200_last_cuda_error(void);
-/* ABI version of this header (3); bumped when a signature changes or an entry point is added. */
+/* ABI version of this header (4); bumped when a signature changes or an entry point is added. */
 int b200_abi_version(void);
 /* Number of kernels this library has launched in this process so far (all entry points). */
 uint64_t b200_launch_count(void);
@@ -162,10 +162,20 @@ int b200_ffn_static_scratch(const void* x, const void* w, const void* bias, cons
  * qkv buffer use {L*3*NH*D, D, 3*NH*D}, which is how the split/transposes of
  * matmul_and_split_qkv (kernels.py:348-367) and the merge of gpt.py:51 cost nothing.
  * D in {16, 32, 64, 128, 256}; scale is normally 1/sqrt(D).
+ * status_word: optional device int*, set non-zero if the tensor-core kernel abandons a bounded wait.
  */
 int b200_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L, int64_t D,
                    const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
-                   const int64_t o_strides[3], float scale, int in_dtype, int out_dtype, void* stream);
+                   const int64_t o_strides[3], float scale, int in_dtype, int out_dtype, int* status_word, void* stream);
+
+/*
+ * Self-test of the bounded waits every tensor-core kernel of this library uses (no reference counterpart): launches
+ * one warp that waits, with the library's own wait routine, on a shared-memory barrier that nothing ever completes.
+ * After limit_cycles SM clock cycles (1 <= limit_cycles <= 4e9) the wait gives up, the kernel writes
+ * B200_ERR_DEVICE_WAIT to *status_word (device int*, must be zero beforehand) and returns normally; the context
+ * stays usable.  Shows on a healthy GPU that a lost signal ends in a status code and not in a hang.
+ */
+int b200_selftest_bounded_wait(int* status_word, int64_t limit_cycles, void* stream);
 
 #ifdef __cplusplus
 }

@@ -32,7 +32,7 @@ def test_library_builds_and_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/b200_gpt.h but not exported"
     assert sorted(_lib.SIGNATURES) == names, "ctypes signature table and header disagree"
     bound = _lib.load()
-    assert bound.b200_abi_version() == 3
+    assert bound.b200_abi_version() == 4
     assert bound.b200_status_string(0) == b"ok"
     assert bound.b200_status_string(6) == b"a kernel abandoned a bounded wait"
 
@@ -50,9 +50,11 @@ def test_argument_checks_need_no_gpu():
     assert lib.b200_layernorm(None, None, None, None, 0, 8, 1e-5, 0, 0, None) == 0  # empty input is a no-op
     assert lib.b200_embedding(None, None, None, None, 2, 9, 10, 8, 4, 0, None, None) == 1  # L > P
     strides = (ctypes.c_int64 * 3)(1, 1, 1)
-    assert lib.b200_attention(None, None, None, None, 1, 1, 4, 24, strides, strides, strides, strides, 1.0, 0, 0, None) == 1
+    assert lib.b200_attention(None, None, None, None, 1, 1, 4, 24, strides, strides, strides, strides, 1.0, 0, 0, None, None) == 1
     assert lib.b200_gemm(None, None, None, None, None, 4, 4, 0, 8, 8, 4, 4, 1, 1, 0, None, None) == 1  # K = 0
     assert lib.b200_ffn(None, None, None, None, None, 0, 4, 4, 4, 0, 0, 1, None, 0, None, None) == 0  # M = 0
+    assert lib.b200_selftest_bounded_wait(None, 1000, None) == 1  # needs a status word
+    assert lib.b200_selftest_bounded_wait(ctypes.c_void_p(256), 0, None) == 1  # and a positive cycle limit
     # row statistics without the product: argmax_out is mandatory, targets and target_logit_out come together,
     # the rounding type is 16-bit, and the workspace is checked before any launch
     assert lib.b200_gemm_argmax_workspace_bytes(100, 1000) == 8 * 128 * 12  # 4 tiles of 256 columns x 2 slices, rows padded to 64
