@@ -187,13 +187,17 @@ def run_reference_arm(args, rank):
         return
     tps, mean_s, threads = cpu_forward_tokens_per_s(args.steps, args.warmup)
     sample = f"{CPU_SAMPLE_BATCH} x {SEQ} tokens of the 512 x 300 batch per step, fp16-rounded operands, fp32 accumulate"
+    hf = cpu_hf_forward_tokens_per_s(steps=1, warmup=1)
     print(json.dumps({
         "impl": "reference", "metric": "gpt2_124m_fwd_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_s * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
         "config": {"workload": "GPT-2 124M forward + tied lm_head, 512 x 300 fp16 (CPU arm: bounded sample per step)",
                    "batch": CPU_SAMPLE_BATCH, "seq_len": SEQ},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
+                         **({"hf_gpt2_fp32": {"value": hf[0], "unit": "tokens/s", "cores": hf[2],
+                                              "what": "transformers GPT2Model (same weights, fp32) + hidden @ wte.T on the same sample"}}
+                            if hf is not None else {})},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
