@@ -1,14 +1,15 @@
 """Benchmark of the GPT-2 forward hot path: tokens/s of a GPT-2 124M forward (tied lm_head
-included) on synthetic 512 x 300 fp16 batches, per GPU (weak scaling over the GPUs of one node).
+included) on ONE synthetic 512 x 300 fp16 batch, split by rows over the GPUs of one node (strong scaling:
+rank r of N runs rows [r * 512 / N, (r + 1) * 512 / N) on a full replica of the weights).
 
     python bench.py [--gpus N] [--steps K] [--warmup W]          # this engine (sm_100a kernels)
-    python bench.py --impl reference [...]                       # CPU restatement of the reference
+    python bench.py --impl reference [...]                       # the plain PyTorch forward on the host cores
 
 One "step" is one forward pass (embedding -> 12 blocks -> final LayerNorm -> lm_head logits) over
-one batch.  Rank 0 prints one JSON line.  `value` is device-timed with the ids resident in HBM;
-`e2e` is the same pass driven from pinned host ids with the argmax ids read back each step.
-Weights are random-init N(0, 0.02) (output projections scaled by 1/sqrt(24)), ids uniform: no
-dataset or checkpoint is involved.
+the batch.  Rank 0 prints one JSON line.  `value` is device-timed with the ids resident in HBM;
+`e2e` is the same pass driven from pinned host ids with the argmax ids (all-gathered over NCCL when N > 1)
+read back each step.  Weights are random-init N(0, 0.02) (output projections scaled by 1/sqrt(24)), ids
+uniform: no dataset or checkpoint is involved.
 """
 
 import argparse
@@ -33,7 +34,9 @@ OTHER_MODELS = {
     "355m": (dict(vocab_size=50257, block_size=1024, n_layer=24, n_head=16, n_embd=1024, dropout=0.1), 256, 1024, torch.bfloat16),
     "1.5b": (dict(vocab_size=50257, block_size=1024, n_layer=48, n_head=25, n_embd=1600, dropout=0.1), 128, 1024, torch.bfloat16),
 }
-CPU_SAMPLE_BATCH = 16  # sequences per CPU-baseline step (the full batch would take minutes per step)
+CPU_SAMPLE_BATCH = 32  # sequences per CPU-baseline step (the full batch would take minutes per step)
+# One-pass ncu capture (DRAM bytes read + written, duration) of the full-size c_fc launch; bench.py only reads it.
+TRAFFIC_FILE = os.path.join("profiles", "gemm_tn_kernel_c_fc_153600x3072x768_fp16_dram.md")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -51,6 +54,21 @@ def make_state_dict(dtype):
     cfg = orc.OracleConfig(**GPT2_SMALL)
     sd = orc.seeded_state_dict(cfg, seed=0, scale_residual_proj=True)
     return cfg, {k: v.to(dtype) for k, v in sd.items()}
+
+
+def measured_traffic():
+    """(bytes per launch, source) of the dominant kernel's launch from the tracked one-pass ncu summary: the line
+    `traffic_bytes_per_launch: <read> + <write>` of TRAFFIC_FILE; (None, reason) if the summary is not there."""
+    path = os.path.join(ROOT, TRAFFIC_FILE)
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.startswith("traffic_bytes_per_launch:"):
+                    read, write = (float(t) for t in line.split(":", 1)[1].split("+"))
+                    return read + write, TRAFFIC_FILE
+    except (OSError, ValueError):
+        pass
+    return None, "no ncu summary of the full-size launch in this tree"
 
 
 def make_ids(batch, seed):
@@ -122,17 +140,21 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU arm
+def use_all_host_threads():
+    """Every host core this process may use: torchrun exports OMP_NUM_THREADS=1 to its workers, which would leave the
+    CPU arm on a single thread."""
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
+
+
 def cpu_forward_tokens_per_s(steps, warmup):
     """The oracle (CPU restatement of the reference's forward + tied lm_head, all host threads)
     on CPU_SAMPLE_BATCH x 300 tokens of the benchmark batch per step."""
     from oracle import gpt2_oracle as orc
 
-    # every host core this process may use: torchrun exports OMP_NUM_THREADS=1 to its workers, which would leave the
-    # CPU arm on a single thread
-    try:
-        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
-    except (AttributeError, OSError):
-        torch.set_num_threads(max(1, os.cpu_count() or 1))
+    use_all_host_threads()
     cfg, sd = make_state_dict(torch.float16)
     ids = make_ids(BATCH, 0)[:CPU_SAMPLE_BATCH]
     times = []
@@ -154,6 +176,7 @@ def cpu_hf_forward_tokens_per_s(steps, warmup):
         from transformers import GPT2Config, GPT2Model
     except Exception:
         return None
+    use_all_host_threads()
     kw = GPT2_SMALL
     hf_cfg = GPT2Config(vocab_size=kw["vocab_size"], n_positions=kw["block_size"], n_embd=kw["n_embd"], n_layer=kw["n_layer"],
                         n_head=kw["n_head"], resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
@@ -182,22 +205,39 @@ def cpu_hf_forward_tokens_per_s(steps, warmup):
     return ids.numel() / mean, mean, torch.get_num_threads()
 
 
+def cpu_baseline_record(steps, warmup, port_steps):
+    """The CPU figures of this workload on the host cores: the plain PyTorch forward the reference measures itself
+    against (transformers' GPT2Model fp32 + hidden @ wte.T; bench.py:26-52 of the reference) as the value, and the
+    rounding-faithful oracle port of the reference's kernels (slower: it emulates fp16 operand rounding) next to it."""
+    sample = f"{CPU_SAMPLE_BATCH} x {SEQ} tokens of the 512 x 300 batch per step"
+    hf = cpu_hf_forward_tokens_per_s(steps=steps, warmup=warmup)
+    port = cpu_forward_tokens_per_s(steps=port_steps, warmup=1) if port_steps > 0 else None
+    if hf is None:  # transformers missing: the port is all there is
+        port = port or cpu_forward_tokens_per_s(steps=steps, warmup=warmup)
+        return {"value": port[0], "unit": "tokens/s", "cores": port[2], "kind": "port", "mean_s_per_step": port[1],
+                "sample": sample + ", oracle port (fp16-rounded operands, fp32 accumulate)"}
+    rec = {"value": hf[0], "unit": "tokens/s", "cores": hf[2], "kind": "port", "mean_s_per_step": hf[1],
+           "sample": sample + f", fp32, {steps} timed passes after {warmup} warm-up",
+           "what": "transformers GPT2Model built from a config with the benchmark's weights, fp32, + hidden @ wte.T + argmax: the plain "
+                   "PyTorch forward the reference benchmarks itself against"}
+    if port is not None:
+        rec["oracle_port"] = {"value": port[0], "unit": "tokens/s", "cores": port[2],
+                              "what": "CPU restatement of the reference's kernels with their rounding points, same sample"}
+    return rec
+
+
 def run_reference_arm(args, rank):
     if rank != 0:
         return
-    tps, mean_s, threads = cpu_forward_tokens_per_s(args.steps, args.warmup)
-    sample = f"{CPU_SAMPLE_BATCH} x {SEQ} tokens of the 512 x 300 batch per step, fp16-rounded operands, fp32 accumulate"
-    hf = cpu_hf_forward_tokens_per_s(steps=1, warmup=1)
+    cpu = cpu_baseline_record(steps=args.steps, warmup=args.warmup, port_steps=1)
+    tps = cpu["value"]
     print(json.dumps({
         "impl": "reference", "metric": "gpt2_124m_fwd_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_s * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
-        "config": {"workload": "GPT-2 124M forward + tied lm_head, 512 x 300 fp16 (CPU arm: bounded sample per step)",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cpu["mean_s_per_step"] * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": {"workload": "GPT-2 124M forward + tied lm_head, 512 x 300 (CPU arm: bounded sample per step)",
                    "batch": CPU_SAMPLE_BATCH, "seq_len": SEQ},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
-                         **({"hf_gpt2_fp32": {"value": hf[0], "unit": "tokens/s", "cores": hf[2],
-                                              "what": "transformers GPT2Model (same weights, fp32) + hidden @ wte.T on the same sample"}}
-                            if hf is not None else {})},
+        "cpu_baseline": cpu,
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -209,7 +249,8 @@ def run_gpu_arm(args, rank, world, local_rank):
 
     from gpt_triton_b200 import _lib
     from gpt_triton_b200 import kernels as K
-    from gpt_triton_b200.gpt import FusedGPT, GPTConfig, executed_fwd_flops
+    from gpt_triton_b200.gpt import FusedGPT, GPTConfig, GraphedForward, executed_fwd_flops
+    from gpt_triton_b200.sharding import gather_equal_rows, gather_rows, shard_bounds
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
@@ -223,9 +264,14 @@ def run_gpu_arm(args, rank, world, local_rank):
     model = model.half().to(dev).eval()
     del sd
 
-    ids_host = make_ids(BATCH, rank).pin_memory()  # every rank its own 512 x 300 batch (weak scaling)
+    # ONE global 512 x 300 batch (the same seeded ids on every rank); rank r runs its contiguous rows of it
+    BATCH = args.global_batch
+    ids_global = make_ids(512, 0)[:BATCH]
+    lo, hi = shard_bounds(BATCH, rank, world)
+    local_batch = hi - lo
+    ids_host = ids_global[lo:hi].contiguous().pin_memory()
     ids_dev = ids_host.to(dev)
-    tokens_per_step = BATCH * SEQ
+    tokens_per_step = BATCH * SEQ  # whole job
 
     def barrier():
         if world > 1:
@@ -239,10 +285,27 @@ def run_gpu_arm(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
+    status = {"code": 0}
+
+    def check_device_status(where):
+        """A kernel that gave up a bounded on-chip wait returns early: its time would be a fast wrong number."""
+        code = K.device_status(dev)
+        if code:
+            status["code"] = code
+            raise RuntimeError(f"{where}: a kernel abandoned a bounded wait (device status {code}); the timing is void")
+
+    def timed_replays(graph, steps):
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            graph.replay()
+        end.record()
+        barrier()
+        return max_over_ranks(start.elapsed_time(end)) / steps
+
     # ---- device-resident throughput ("value"): the forward + lm_head captured once in a CUDA graph (the library's
     # GraphedForward) and replayed, so that host-side launch jitter on a shared box cannot starve the GPU
-    from gpt_triton_b200.gpt import GraphedForward
-
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
     if rank == 0:
         sampler.start()  # only rank 0's GPU is reported; eight nvidia-smi processes at once slow each other down
@@ -254,26 +317,20 @@ def run_gpu_arm(args, rank, world, local_rank):
     launches_per_forward = (lib.b200_launch_count() - launches_before_capture) // 2  # one warm-up pass + the captured pass
     for _ in range(max(1, args.warmup)):
         fwd.graph.replay()
-    barrier()
     sampler.mark_begin()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        fwd.graph.replay()
-    end.record()
-    barrier()
+    ms_per_step = timed_replays(fwd.graph, args.steps)
     sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
+    check_device_status("timed forward")
     launches = launches_per_forward * args.steps
-    ms_total = max_over_ranks(start.elapsed_time(end))
-    ms_per_step = ms_total / args.steps
-    value = world * tokens_per_step / (ms_per_step * 1e-3)
+    value = tokens_per_step / (ms_per_step * 1e-3)
     del fwd
 
-    # ---- end to end: pinned host ids in, argmax ids (from the lm_head epilogue) out, every step
+    # ---- end to end: pinned host ids in, argmax ids (from the lm_head epilogue, all ranks' rows gathered) out, every step
     out_host = torch.empty((BATCH, SEQ), dtype=torch.int64).pin_memory()
     e2e_fwd = GraphedForward(model, ids_dev, what="logits_and_next_ids", warmup=1)
-    gathered = None
+    gathered = torch.empty((BATCH, SEQ), device=dev, dtype=torch.int64) if world > 1 else None
+    even = BATCH % world == 0
 
     def e2e_step():
         nonlocal gathered
@@ -281,36 +338,54 @@ def run_gpu_arm(args, rank, world, local_rank):
         e2e_fwd.graph.replay()
         am = e2e_fwd.outputs[1]
         if world > 1:
-            if gathered is None:
-                gathered = torch.empty((world,) + tuple(am.shape), device=dev, dtype=am.dtype)
-            dist.all_gather_into_tensor(gathered, am)  # 8 bytes per token cross NVLink, one collective, no staging copies
-        out_host.copy_(am, non_blocking=True)
+            # 8 bytes per token cross NVLink: one NCCL all-gather of the ids, straight into the result buffer
+            if even:
+                gather_equal_rows(am, out=gathered)
+            else:
+                gathered = gather_rows(am, BATCH)
+            out_host.copy_(gathered, non_blocking=True)
+        else:
+            out_host.copy_(am, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(max(1, args.warmup // 2)):
         e2e_step()
     barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
         e2e_step()
     end.record()
     barrier()
     e2e_ms = max_over_ranks(start.elapsed_time(end)) / args.steps
-    e2e_value = world * tokens_per_step / (e2e_ms * 1e-3)
+    e2e_value = tokens_per_step / (e2e_ms * 1e-3)
+    check_device_status("end-to-end steps")
+    # every rank holds the whole batch's ids; its own rows are what its own forward produced
+    assert torch.equal(out_host[lo:hi], e2e_fwd.outputs[1].cpu()), "gathered ids do not contain this rank's rows"
+    ids_checksum = int(out_host.sum().item())
+    if world > 1:
+        t = torch.tensor([ids_checksum, -ids_checksum], device=dev, dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        assert t[0].item() == -t[1].item(), "ranks disagree on the gathered ids"
     del e2e_fwd
 
     # ---- for information: the same forward with the lm_head reduced to its row argmax inside the GEMM epilogue
     # (FusedGPT.next_ids: the [tokens, vocab] logits are never written); not the headline workload
     ids_fwd = GraphedForward(model, ids_dev, what="next_ids", warmup=1)
     ids_fwd.graph.replay()
-    barrier()
-    start.record()
-    for _ in range(args.steps):
-        ids_fwd.graph.replay()
-    end.record()
-    barrier()
-    ids_only_ms = max_over_ranks(start.elapsed_time(end)) / args.steps
+    ids_only_ms = timed_replays(ids_fwd.graph, args.steps)
     del ids_fwd
+
+    # ---- for information at N > 1: the replica figure (every rank a whole 512 x 300 batch of its own, no split)
+    weak = None
+    if world > 1:
+        full_ids = make_ids(512, rank)[:BATCH].to(dev)
+        wfwd = GraphedForward(model, full_ids, what="logits", warmup=1)
+        wfwd.graph.replay()
+        weak_ms = timed_replays(wfwd.graph, max(2, args.steps // 2))
+        weak = {"value": world * BATCH * SEQ / (weak_ms * 1e-3), "unit": "tokens/s", "ms_per_step": weak_ms,
+                "what": "weak scaling: every GPU runs its own 512 x 300 batch (N times the work of the headline)"}
+        del wfwd, full_ids
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA events around every GEMM launch
     # of further forward passes, on the stream the kernels are launched on.  The other operators are
@@ -351,6 +426,7 @@ def run_gpu_arm(args, rank, world, local_rank):
     finally:
         for name, fn in orig.items():
             setattr(K, name, fn)
+    check_device_status("per-operator probe passes")
     # Per shape, the MEDIAN launch duration (a host stall on a shared box can leave the GPU idle inside one bracket)
     by_shape = {}
     for m, n, k, s, e in records:
@@ -369,42 +445,46 @@ def run_gpu_arm(args, rank, world, local_rank):
         breakdown[kind] = statistics.median(times) * len(times) / probe_steps
     breakdown["unattributed"] = ms_per_step - sum(breakdown.values())
 
-    flops = executed_fwd_flops(gcfg, BATCH, SEQ)
+    flops = executed_fwd_flops(gcfg, local_batch, SEQ)  # per GPU
     per_gpu_flops_s = flops / (ms_per_step * 1e-3)
 
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
-        tps, mean_s, threads = cpu_forward_tokens_per_s(steps=2, warmup=1)
-        cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": f"{CPU_SAMPLE_BATCH} x {SEQ} tokens of the batch, 2 timed passes after 1 warm-up ({mean_s:.2f} s each)"}
-        hf = cpu_hf_forward_tokens_per_s(steps=1, warmup=1)
-        if hf is not None:
-            cpu["hf_gpt2_fp32"] = {"value": hf[0], "unit": "tokens/s", "cores": hf[2],
-                                   "what": "transformers GPT2Model (same weights, fp32) + hidden @ wte.T on the same sample"}
+        cpu = cpu_baseline_record(steps=2, warmup=1, port_steps=1)
 
     if rank == 0:
+        traffic, traffic_source = measured_traffic()
+        sm_mhz = clocks.get("sm_mhz") if clocks else None
         print(json.dumps({
             "metric": "gpt2_124m_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp16", "data": "synthetic",
-            "config": {"workload": "GPT-2 124M forward + tied lm_head (logits written), 512 x 300 tokens per GPU, fp16 storage, fp32 accumulate",
-                       "batch_per_gpu": BATCH, "seq_len": SEQ, "global_batch": BATCH * world, "parallelism": f"batch-sharded replicas x{world}",
-                       "l2": "no flush: each step streams > 20 GB of activations and logits, far beyond the 126 MB L2",
+            "config": {"workload": f"GPT-2 124M forward + tied lm_head (logits written), ONE {BATCH} x 300 batch split by rows over the GPUs, "
+                                   "fp16 storage, fp32 accumulate",
+                       "global_batch": BATCH, "batch_per_gpu": local_batch, "seq_len": SEQ,
+                       "parallelism": f"batch rows sharded x{world}, full weight replica per GPU",
+                       "layer_norm": "folded into c_attn / c_fc (statistics from the producing kernel); final LayerNorm is a kernel",
+                       "l2": "no flush: each step streams several GB of activations and logits per GPU, far beyond the 126 MB L2",
                        "flop_per_step_per_gpu": flops},
             "breakdown_ms_per_step": breakdown,
+            "ms_per_step_x_sm_mhz": ms_per_step * sm_mhz if sm_mhz else None,
             "mfu": {"of_spec_2250": per_gpu_flops_s / 2250e12, f"of_{peak_kind}_sustained": per_gpu_flops_s / (peak_tflops * 1e12)},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ids_host.numel() * 8,
                     "d2h_bytes_per_step": out_host.numel() * 8,
-                    "collective": "all_gather of argmax ids" if world > 1 else None},
-            "next_ids_only": {"value": world * tokens_per_step / (ids_only_ms * 1e-3), "unit": "tokens/s", "ms_per_step": ids_only_ms,
+                    "collective": "NCCL all_gather_into_tensor of the argmax ids (8 B/token)" if world > 1 else None,
+                    "ids_checksum": ids_checksum},
+            "next_ids_only": {"value": tokens_per_step / (ids_only_ms * 1e-3), "unit": "tokens/s", "ms_per_step": ids_only_ms,
                               "note": "same forward, greedy ids out of the lm_head epilogue, logits not written; informational"},
-            "gpu_launches": int(launches), "launch_mode": f"CUDA graph replay, {launches_per_forward} library kernels per forward",
-            "roofline": {"kernel": "gemm_tn_kernel (tcgen05, all five GEMM shapes of the forward)", "bound": "tensor",
+            "weak_per_gpu": weak,
+            "device_status": status["code"],
+            "gpu_launches": int(launches), "launch_mode": f"CUDA graph replay, {launches_per_forward} library kernels per forward, "
+                                                          f"programmatic dependent launch {'on' if os.environ.get('B200GPT_PDL', '0') == '1' else 'off'}",
+            "roofline": {"kernel": "gemm_tn_kernel (tcgen05, all GEMM shapes of the forward)", "bound": "tensor",
                          "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved_tflops / peak_tflops,
                          "peak_source": f"{peak_kind}: cuBLAS bf16 sustained",
-                         # DRAM bytes of one c_fc launch (153600 x 3072 x 768): dram read+write of the ncu capture of a
-                         # 32768-row launch (profiles/gemm_tn_kernel_bias_gelu_32768x3072x768_fp16.md) scaled by 153600/32768
-                         "traffic": (55.15e6 + 146.48e6) * 153600 / 32768, "traffic_algorithmic": 2.0 * (153600 * 768 + 768 * 3072 + 153600 * 3072),
+                         # DRAM bytes of one full-size c_fc launch (153600 x 3072 x 768) as ncu counted them
+                         "traffic": traffic, "traffic_source": traffic_source,
+                         "traffic_algorithmic": 2.0 * (153600 * 768 + 768 * 3072 + 153600 * 3072),
                          "per_shape": detail},
             "cpu_baseline": cpu,
             "clocks": clocks,
@@ -457,6 +537,33 @@ def run_sweep(args):
         ms = timed(lambda: K.fused_ffn(x, pw, bias=b, add_gelu=True, out=out))
         report("gemm_bias_gelu", ms, "tensor", 2.0 * M * 768 * 3072, float(peaks["bf16_tflops"]), {"M": M, "K": 768, "N": 3072})
         del x, out
+    if which in ("gemm_ln", "all"):
+        # the same shape as the forward runs it: LayerNorm folded in (raw rows + their statistics), bias + GELU
+        x = torch.randn((M, 768), generator=g).half().to(dev)
+        w = (torch.randn((768, 3072), generator=g) * 0.02).half().to(dev)
+        b = torch.randn(3072, generator=g).half().to(dev)
+        gamma = (1 + 0.1 * torch.randn(768, generator=g)).half().to(dev)
+        beta = (0.1 * torch.randn(768, generator=g)).half().to(dev)
+        fw = K.fold_layer_norm(w, gamma, beta, b)
+        mom = K.row_stats(x)
+        out = torch.empty((M, 3072), device=dev, dtype=torch.float16)
+        ms = timed(lambda: K.fused_ffn(x, fw, add_gelu=True, ln_stats=mom, out=out))
+        report("gemm_layernorm_bias_gelu", ms, "tensor", 2.0 * M * 768 * 3072, float(peaks["bf16_tflops"]), {"M": M, "K": 768, "N": 3072})
+        del x, out, mom
+    if which in ("gemm_res", "all"):
+        # attention c_proj as the forward runs it: bias + residual, row statistics of the output emitted
+        x = torch.randn((M, 768), generator=g).half().to(dev)
+        w = (torch.randn((768, 768), generator=g) * 0.02).half().to(dev)
+        b = torch.randn(768, generator=g).half().to(dev)
+        r = torch.randn((M, 768), generator=g).half().to(dev)
+        pw = K.pack_weight(w)
+        out = torch.empty((M, 768), device=dev, dtype=torch.float16)
+        for name, fn in (("gemm_bias_residual", lambda: K.fused_ffn(x, pw, bias=b, residual=r, out=out)),
+                         ("gemm_bias_residual_row_stats", lambda: K.fused_ffn(x, pw, bias=b, residual=r, out=out, return_row_stats=True))):
+            ms = timed(fn)
+            report(name, ms, "tensor", 2.0 * M * 768 * 768, float(peaks["bf16_tflops"]),
+                   {"M": M, "K": 768, "N": 768, "hbm_gbs": 3.0 * M * 768 * 2 / (ms * 1e-3) / 1e9})
+        del x, out, r
     if which in ("lm_head", "all"):
         x = torch.randn((M, 768), generator=g).half().to(dev)
         wte = (torch.randn((50257, 768), generator=g) * 0.02).half().to(dev)
@@ -488,6 +595,57 @@ def run_sweep(args):
             report(f"attention_S{S}", ms, "tensor", 4.0 * B * 12 * 64 * S * (S + 1) / 2, float(peaks["bf16_tflops"]),
                    {"B": B, "H": 12, "D": 64, "S": S, "hbm_gbs": 4.0 * B * S * 768 * 2 / (ms * 1e-3) / 1e9})
             del qkv, q, k, v
+
+
+def run_gap_table(args):
+    """Where one replayed forward spends its time between kernels: kernel start/end records of ONE CUDA-graph replay
+    of the headline forward (torch.profiler's CUPTI activity records: no counters, no kernel is serialised or
+    replayed), summed per kernel name, with the idle time between consecutive kernels (negative when programmatic
+    dependent launch lets a kernel's set-up start under its predecessor's tail).  A diagnosis, not a benchmark value."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from gpt_triton_b200.gpt import FusedGPT, GPTConfig, GraphedForward
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    _, sd = make_state_dict(torch.float16)
+    model = FusedGPT(GPTConfig(**GPT2_SMALL))
+    model.load_state_dict(sd)
+    model = model.half().to(dev).eval()
+    batch = args.global_batch
+    ids = make_ids(BATCH, 0)[:batch].to(dev)
+    fwd = GraphedForward(model, ids, what="logits", warmup=3)
+    for _ in range(5):
+        fwd.graph.replay()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(10):
+        fwd.graph.replay()
+    e.record()
+    torch.cuda.synchronize()
+    plain_ms = s.elapsed_time(e) / 10
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        fwd.graph.replay()
+        torch.cuda.synchronize()
+    recs = sorted(((ev.time_range.start, ev.time_range.end, ev.name) for ev in prof.events()
+                   if ev.device_type == torch.autograd.DeviceType.CUDA and ev.time_range.end > ev.time_range.start), key=lambda r: r[0])
+    span = recs[-1][1] - recs[0][0]
+    busy = sum(r[1] - r[0] for r in recs)
+    gaps = [(b[0] - a[1], a[2][:60], b[2][:60]) for a, b in zip(recs, recs[1:])]
+    by_name = {}
+    for st, en, name in recs:
+        key = name.split("(")[0][:90]
+        n, t = by_name.get(key, (0, 0.0))
+        by_name[key] = (n + 1, t + (en - st))
+    print(json.dumps({
+        "what": "one CUDA-graph replay of the forward + lm_head under CUPTI activity tracing", "batch": batch, "seq_len": SEQ,
+        "kernels": len(recs), "span_ms": span / 1e3, "sum_of_kernel_durations_ms": busy / 1e3,
+        "idle_between_kernels_ms": sum(g[0] for g in gaps if g[0] > 0) / 1e3, "overlap_ms": -sum(g[0] for g in gaps if g[0] < 0) / 1e3,
+        "median_gap_us": statistics.median(g[0] for g in gaps), "replay_ms_without_profiler": plain_ms,
+        "per_kernel": {k: {"launches": n, "total_ms": t / 1e3} for k, (n, t) in sorted(by_name.items(), key=lambda kv: -kv[1][1])},
+        "largest_gaps_us": [{"gap_us": g[0], "after": g[1], "before": g[2]} for g in sorted(gaps, key=lambda g: -g[0])[:5]],
+    }))
 
 
 def run_other_model(args):
@@ -533,12 +691,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--sweep", default=None, choices=["gemm", "lm_head", "layernorm", "embedding", "attention", "all"],
+    ap.add_argument("--sweep", default=None, choices=["gemm", "gemm_ln", "gemm_res", "lm_head", "layernorm", "embedding", "attention", "all"],
                     help="time single kernels at the kernel-sweep shapes instead of the forward")
     ap.add_argument("--rows", type=int, default=0, help="--sweep: rows (tokens) instead of 153600")
     ap.add_argument("--batch", type=int, default=0, help="--sweep attention: batch instead of 512")
     ap.add_argument("--model", default=None, choices=sorted(OTHER_MODELS), help="time a larger GPT-2 instead of the 124M headline")
+    ap.add_argument("--global-batch", type=int, default=BATCH,
+                    help="sequences in the global batch (default 512, the headline; 64 is what one of 8 GPUs runs)")
+    ap.add_argument("--gap-table", action="store_true", help="per-kernel time and idle gaps of one replayed forward (diagnosis)")
     args = ap.parse_args()
+    if args.gap_table:
+        run_gap_table(args)
+        return
     if args.sweep:
         run_sweep(args)
         return

@@ -24,6 +24,12 @@ SIGNATURES = {
     "b200_abi_version": (c_int, []),
     "b200_launch_count": (ctypes.c_uint64, []),
     "b200_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_void_p, c_void_p]),
+    "b200_embedding_ln_stats": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_void_p, c_float, c_void_p, c_void_p,
+                                        c_void_p]),
+    "b200_row_ln_stats": (c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_float, c_int, c_void_p]),
+    "b200_fold_layernorm": (c_int, [c_void_p] * 8 + [c_i64, c_i64, c_i64, c_int, c_void_p]),
+    "b200_gemm_ln_workspace_bytes": (c_size_t, [c_i64, c_i64]),
+    "b200_gemm_ln": (c_int, [c_void_p] * 5 + [c_i64] * 7 + [c_int, c_int, c_int] + [c_void_p] * 5 + [c_float, c_void_p, c_size_t, c_void_p, c_void_p]),
     "b200_layernorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_float, c_int, c_int, c_void_p]),
     "b200_pack_operand": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_void_p]),
     "b200_gemm": (c_int, [c_void_p] * 5 + [c_i64] * 7 + [c_int, c_int, c_int, c_void_p, c_void_p]),

@@ -2,6 +2,8 @@
 // composition of the kernels; no kernel code lives here.
 #include "common.cuh"
 
+#include <stdint.h>
+
 namespace {
 thread_local cudaError_t g_last_cuda = cudaSuccess;
 int note(int st) {
@@ -14,6 +16,7 @@ int note(int st) {
 bool valid_dtype(int dt) { return dt == B200_F32 || dt == B200_F16 || dt == B200_BF16; }
 size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 bool direct_operand_ok(int dtype, int64_t K) { return dtype != B200_F32 && K % 8 == 0; }
+constexpr int64_t kMaxExtent = 0x7fffffffLL - 256;  // largest M, N or K the GEMM kernel indexes
 }  // namespace
 
 extern "C" {
@@ -33,7 +36,7 @@ const char* b200_status_string(int status) {
 
 const char* b200_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
 
-int b200_abi_version(void) { return 4; }
+int b200_abi_version(void) { return 5; }
 
 uint64_t b200_launch_count(void) { return b200::launches_so_far(); }
 
@@ -43,7 +46,45 @@ int b200_embedding(const int64_t* ids, const void* wte, const void* wpe, void* o
   if (L > P) return B200_ERR_BAD_ARGUMENT;
   if (B * L == 0 || H == 0) return B200_OK;
   if (!ids || !wte || !wpe || !out) return B200_ERR_BAD_ARGUMENT;
-  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, (cudaStream_t)stream));
+  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, nullptr, nullptr, 0.f, (cudaStream_t)stream));
+}
+
+int b200_embedding_ln_stats(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t B, int64_t L, int64_t V,
+                            int64_t P, int64_t H, int dtype, int* bad_id_flag, float eps, float* ln_stats_out, void* ln_ext_out, void* stream) {
+  if (B < 0 || L < 0 || V < 1 || P < 1 || H < 0 || !valid_dtype(dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (L > P) return B200_ERR_BAD_ARGUMENT;
+  if (B * L == 0 || H == 0) return B200_OK;
+  if (!ids || !wte || !wpe || !out || !ln_stats_out || (reinterpret_cast<uintptr_t>(ln_stats_out) & 7) || (reinterpret_cast<uintptr_t>(ln_ext_out) & 15))
+    return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, ln_stats_out, ln_ext_out, eps, (cudaStream_t)stream));
+}
+
+int b200_row_ln_stats(const void* x, float* ln_stats_out, void* ln_ext_out, int64_t M, int64_t H, float eps, int dtype, void* stream) {
+  if (M < 0 || H < 0 || !valid_dtype(dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (M == 0 || H == 0) return B200_OK;
+  if (!x || !ln_stats_out || (reinterpret_cast<uintptr_t>(ln_stats_out) & 7) || (reinterpret_cast<uintptr_t>(ln_ext_out) & 15)) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_row_ln_stats(x, ln_stats_out, ln_ext_out, M, H, eps, dtype, (cudaStream_t)stream));
+}
+
+int b200_fold_layernorm(const void* w, const void* gamma, const void* beta, const void* bias, void* packed, float* colsum, float* bias_out,
+                        void* w_ext, int64_t K, int64_t N, int64_t ld_packed, int dtype, void* stream) {
+  if (K < 0 || N < 0 || !valid_dtype(dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (dtype == B200_F32) return B200_ERR_UNSUPPORTED;
+  if (K == 0 || N == 0) return B200_OK;
+  if (!w || !gamma || !beta || !packed || !colsum || !bias_out || !w_ext || ld_packed < K || (reinterpret_cast<uintptr_t>(w_ext) & 15))
+    return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_fold_layernorm(w, gamma, beta, bias, packed, colsum, bias_out, w_ext, K, N, ld_packed, dtype, (cudaStream_t)stream));
+}
+
+size_t b200_gemm_ln_workspace_bytes(int64_t M, int64_t N) { return b200::gemm_ln_workspace_bytes(M, N); }
+
+int b200_gemm_ln(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                 int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype, int add_gelu, const float* ln_stats,
+                 const void* ln_ext, const void* w_ext, float* ln_stats_out, void* ln_ext_out, float eps, void* workspace, size_t workspace_bytes,
+                 int* status_word, void* stream) {
+  if (!valid_dtype(io_dtype)) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_gemm_ln(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, io_dtype, add_gelu, ln_stats, ln_ext,
+                                   w_ext, ln_stats_out, ln_ext_out, eps, workspace, workspace_bytes, status_word, (cudaStream_t)stream));
 }
 
 int b200_layernorm(const void* x, const void* w, const void* b, void* out, int64_t M, int64_t H, float eps,
@@ -91,6 +132,7 @@ int b200_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t M
 
 size_t b200_ffn_workspace_bytes(int64_t M, int64_t N, int64_t K, int w_is_nk, int dtype) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > kMaxExtent || N > kMaxExtent || K > kMaxExtent) return SIZE_MAX;  // b200_ffn rejects such a problem; no figure can be met
   const size_t kp = (size_t)((K + 7) / 8 * 8);
   size_t bytes = 0;
   if (!direct_operand_ok(dtype, K)) bytes += round256((size_t)M * kp * 2);
@@ -104,6 +146,7 @@ int b200_ffn(const void* x, const void* w, const void* bias, const void* residua
   if (!valid_dtype(dtype) || M < 0 || N < 0 || K < 0) return B200_ERR_BAD_ARGUMENT;
   if (M == 0 || N == 0) return B200_OK;
   if (K == 0 || !x || !w || !out || ld_out < N) return B200_ERR_BAD_ARGUMENT;
+  if (M > kMaxExtent || N > kMaxExtent || K > kMaxExtent) return B200_ERR_BAD_ARGUMENT;  // before any size arithmetic or packing launch
   cudaStream_t s = (cudaStream_t)stream;
   const int op_dtype = dtype == B200_BF16 ? B200_BF16 : B200_F16;
   const int64_t kp = (K + 7) / 8 * 8;

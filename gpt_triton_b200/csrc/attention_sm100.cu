@@ -3,17 +3,21 @@
 // reference, and both operands of one MMA must have the same format, so a bf16 V tile is converted to
 // fp16 in place (exact in fp16's normal range) by the softmax warps before P V.
 //
-// Work item = 128 query rows of one (batch, head).  Persistent CTAs (two per SM) walk the items,
+// Work item = 128 query rows of one (batch, head).  Persistent CTAs (three per SM) walk the items,
 // longest first.  Per CTA:
-//   warp 0      TMA producer: the 128x64 Q tile (double-buffered) and, per 64-key block, the K and
-//               V tiles (3-stage ring), all 128-byte swizzled, straight out of the strided q/k/v
-//               views (4-D tensor maps: head_dim, row, head, batch); every CTA issues its own loads
-//   warp 1      tcgen05.mma issuer: S = Q K^T (128x64, fp32, tensor memory, double-buffered, issued
-//               one block ahead) and PV = P V (128x64, fresh accumulator per block, double-buffered)
+//   warp 0      TMA producer: the 128x64 Q tile and, per 64-key block, the K and V tiles (2-stage ring),
+//               all 128-byte swizzled, straight out of the strided q/k/v views (4-D tensor maps:
+//               head_dim, row, head, batch); every CTA issues its own loads
+//   warp 1      tcgen05.mma issuer: S = Q K^T (128x64, fp32, tensor memory) and O (+)= P V, which
+//               accumulates in tensor memory over the key blocks of an item
 //   warps 2-5   softmax: one thread per query row.  Reads S from tensor memory, keeps the running
 //               maximum/denominator in fp32, writes P = exp(s - max) rounded to fp16 into shared
-//               memory in the swizzled K-major operand layout, and folds the previous block's PV
-//               into its fp32 output row: o = o * exp(m_old - m_new) + PV.
+//               memory in the swizzled K-major operand layout and, when the running maximum of any of
+//               its rows moved, rescales its 32 rows of O in tensor memory (load, multiply, store)
+//               before P V of the block is issued:  o = o * exp(m_old - m_new) + P V.
+// The output row never lives in registers across blocks, which keeps a softmax thread near 100
+// registers: three CTAs (twelve softmax warps) fit an SM, and it is the number of softmax warps in
+// flight that keeps the special-function unit, the limiter of attention at head size 64, busy.
 // The softmax runs over 64-key blocks with P rounded relative to the running maximum of each
 // block, which is the arithmetic of the reference's flash_attention_v1 kernel (kernels.py:417-474
 // of the reference); blocks above the diagonal are skipped.  Every mbarrier wait is bounded.
@@ -29,15 +33,16 @@ using namespace sm100;
 constexpr int D = 64;
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_N = 64;
-constexpr int KV_STAGES = 3;
+constexpr int KV_STAGES = 2;
 constexpr int Q_BYTES = BLOCK_M * D * 2;        // 16 KB
 constexpr int KV_TILE_BYTES = BLOCK_N * D * 2;  // 8 KB each for K and V
 constexpr int KV_STAGE_BYTES = 2 * KV_TILE_BYTES;
 constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;  // 16 KB
 constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 256;  // S[2] (64 columns each) + PV[2] (64 columns each)
+constexpr int CTAS_PER_SM = 3;
+constexpr int TMEM_COLS = 128;  // S (64 columns) + O (64 columns)
 constexpr int CTRL_BYTES = 256;
-constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES + 1024 + CTRL_BYTES;
+constexpr int SMEM_BYTES = Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES + 1024 + CTRL_BYTES;
 
 struct Params {
   void* out;
@@ -117,8 +122,20 @@ __device__ __forceinline__ uint32_t pack_out<__nv_bfloat16>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]),
+        "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 template <typename T>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+__global__ void __launch_bounds__(NUM_THREADS, CTAS_PER_SM)
 attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, Params p, uint32_t idesc_s, uint32_t idesc_pv) {
   constexpr bool IS_FP16 = DType<T>::code == B200_F16;
@@ -126,22 +143,20 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  const uint32_t smem_q = base;                                 // [2][128][64]
-  const uint32_t smem_kv = smem_q + 2 * Q_BYTES;                // [KV_STAGES]{K[64][64], V[64][64]}
+  const uint32_t smem_q = base;                                  // [128][64]
+  const uint32_t smem_kv = smem_q + Q_BYTES;                     // [KV_STAGES]{K[64][64], V[64][64]}
   const uint32_t smem_p = smem_kv + KV_STAGES * KV_STAGE_BYTES;  // [128][64] fp16
-  uint8_t* ctrl = smem + 2 * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES;
+  uint8_t* ctrl = smem + Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES;
   const uint32_t bars = smem_u32(ctrl);
-  const uint32_t bar_q_full = bars;                  // [2]
-  const uint32_t bar_q_empty = bars + 16;            // [2]
-  const uint32_t bar_kv_full = bars + 32;            // [KV_STAGES]
-  const uint32_t bar_kv_empty = bar_kv_full + 8 * KV_STAGES;
-  const uint32_t bar_s_full = bar_kv_empty + 8 * KV_STAGES;  // [2]
-  const uint32_t bar_s_empty = bar_s_full + 16;      // [2]
-  const uint32_t bar_p_full = bar_s_empty + 16;      // [1]
-  const uint32_t bar_p_empty = bar_p_full + 8;       // [1]
-  const uint32_t bar_pv_full = bar_p_empty + 8;      // [2]
-  const uint32_t bar_pv_empty = bar_pv_full + 16;    // [2]
-  constexpr int BAR_BYTES = 32 + 16 * KV_STAGES + 16 + 16 + 8 + 8 + 16 + 16;
+  const uint32_t bar_q_full = bars;                             // Q tile of the current item has landed
+  const uint32_t bar_q_empty = bars + 8;                        // every S of the item has been computed: Q may be overwritten
+  const uint32_t bar_kv_full = bars + 16;                       // [KV_STAGES]
+  const uint32_t bar_kv_empty = bar_kv_full + 8 * KV_STAGES;    // [KV_STAGES]
+  const uint32_t bar_s_full = bar_kv_empty + 8 * KV_STAGES;     // S of a block is in tensor memory
+  const uint32_t bar_s_empty = bar_s_full + 8;                  // the four softmax warps have read it
+  const uint32_t bar_p_full = bar_s_empty + 8;                  // P of a block is in shared memory and O has been rescaled
+  const uint32_t bar_pv_done = bar_p_full + 8;                  // P V of a block has been accumulated: P is free, O is current
+  constexpr int BAR_BYTES = 16 + 16 * KV_STAGES + 32;
   static_assert(BAR_BYTES + 16 <= CTRL_BYTES, "control block too small");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + BAR_BYTES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + BAR_BYTES + 8);
@@ -152,20 +167,16 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int64_t n_items = (int64_t)n_qt * bh_total;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_q_full + 8 * i, 1);
-      mbar_init(bar_q_empty + 8 * i, 1);
-      mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_s_empty + 8 * i, 4);
-      mbar_init(bar_pv_full + 8 * i, 1);
-      mbar_init(bar_pv_empty + 8 * i, 4);
-    }
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_empty, 1);
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(bar_kv_full + 8 * i, 1);
       mbar_init(bar_kv_empty + 8 * i, 1);
     }
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_s_empty, 4);
     mbar_init(bar_p_full, 4);
-    mbar_init(bar_p_empty, 1);
+    mbar_init(bar_pv_done, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
@@ -178,8 +189,11 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;         // S[buf] at columns buf*64
-  const uint32_t tmem_pv = tmem_base + 128;  // PV[buf] at columns 128 + buf*64
+  // set-up done (own shared and tensor memory only); global memory from here on
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t tmem_s = tmem_base;            // S: columns [0, 64)
+  const uint32_t tmem_o = tmem_base + BLOCK_N;  // O: columns [64, 128)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -188,10 +202,9 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       bool alive = true;
       for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
         const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
-        const uint32_t qb = qi & 1;
-        if (!mbar_wait(bar_q_empty + 8 * qb, ((qi >> 1) & 1) ^ 1u, abort_flag, p.status_word, 11)) break;
-        mbar_arrive_expect_tx(bar_q_full + 8 * qb, Q_BYTES);
-        tma_load_4d(smem_q + qb * Q_BYTES, &map_q, bar_q_full + 8 * qb, 0, p.q_head_inner ? it.h : it.q0, p.q_head_inner ? it.q0 : it.h, it.b);
+        if (!mbar_wait(bar_q_empty, (qi & 1) ^ 1u, abort_flag, p.status_word, 11)) break;
+        mbar_arrive_expect_tx(bar_q_full, Q_BYTES);
+        tma_load_4d(smem_q, &map_q, bar_q_full, 0, p.q_head_inner ? it.h : it.q0, p.q_head_inner ? it.q0 : it.h, it.b);
         ++qi;
         for (int j = 0; j < it.nblk; ++j) {
           const uint32_t st = ki % KV_STAGES;
@@ -211,41 +224,37 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       uint32_t qi = 0, ks = 0, kp = 0, si = 0, pi = 0;
       bool alive = true;
-      // S_{next} = Q . K^T into S[si & 1]
-      auto issue_s = [&](uint32_t qb) -> bool {
+      // S_next = Q . K^T: needs the block's K/V stage and the softmax warps to be done with the previous S
+      auto issue_s = [&]() -> bool {
         const uint32_t st = ks % KV_STAGES;
         if (!mbar_wait(bar_kv_full + 8 * st, (ks / KV_STAGES) & 1, abort_flag, p.status_word, 13)) return false;
-        const uint32_t sb = si & 1;
-        if (!mbar_wait(bar_s_empty + 8 * sb, ((si >> 1) & 1) ^ 1u, abort_flag, p.status_word, 14)) return false;
+        if (!mbar_wait(bar_s_empty, (si & 1) ^ 1u, abort_flag, p.status_word, 14)) return false;
         tc_fence_after();
-        const uint64_t da = desc_kmajor(smem_q + qb * Q_BYTES);
+        const uint64_t da = desc_kmajor(smem_q);
         const uint64_t db = desc_kmajor(smem_kv + st * KV_STAGE_BYTES);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s + sb * BLOCK_N, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc_s, (uint32_t)(k != 0));
-        umma_commit(bar_s_full + 8 * sb);
+        for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc_s, (uint32_t)(k != 0));
+        umma_commit(bar_s_full);
         ++si;
         ++ks;
         return true;
       };
       for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
         const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
-        const uint32_t qb = qi & 1;
-        if (!mbar_wait(bar_q_full + 8 * qb, (qi >> 1) & 1, abort_flag, p.status_word, 15)) break;
-        if (!issue_s(qb)) break;
+        if (!mbar_wait(bar_q_full, qi & 1, abort_flag, p.status_word, 15)) break;
+        if (!issue_s()) break;
         for (int j = 0; j < it.nblk; ++j) {
           if (j + 1 < it.nblk) {
-            if (!issue_s(qb)) {
+            if (!issue_s()) {
               alive = false;
               break;
             }
           } else {
-            umma_commit(bar_q_empty + 8 * qb);  // every S of this item is issued: Q is free once they finish
+            umma_commit(bar_q_empty);  // every S of this item is issued: Q is free once they finish
           }
-          // PV_j = P . V_j into PV[pi & 1]
+          // O (+)= P_j . V_j : P written, O rescaled (and, for bf16 storage, V converted) by the softmax warps
           const uint32_t st = kp % KV_STAGES;
-          const uint32_t ob = pi & 1;
-          if (!mbar_wait(bar_p_full, pi & 1, abort_flag, p.status_word, 16) ||
-              !mbar_wait(bar_pv_empty + 8 * ob, ((pi >> 1) & 1) ^ 1u, abort_flag, p.status_word, 17)) {
+          if (!mbar_wait(bar_p_full, pi & 1, abort_flag, p.status_word, 16)) {
             alive = false;
             break;
           }
@@ -255,11 +264,10 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int k = 0; k < BLOCK_N / 16; ++k) {
             // A: +16 keys = +32 bytes inside the swizzled row; B: +16 keys = two 8-key groups = +2048 bytes
-            umma_f16(tmem_pv + ob * D, da + (uint64_t)(2 * k), db + (uint64_t)(128 * k), idesc_pv, (uint32_t)(k != 0));
+            umma_f16(tmem_o, da + (uint64_t)(2 * k), db + (uint64_t)(128 * k), idesc_pv, (uint32_t)((j | k) != 0));
           }
-          umma_commit(bar_pv_full + 8 * ob);
+          umma_commit(bar_pv_done);
           umma_commit(bar_kv_empty + 8 * st);
-          umma_commit(bar_p_empty);
           ++pi;
           ++kp;
         }
@@ -273,6 +281,8 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t p_row = smem_p + (uint32_t)r_in_tile * 128u;
     const uint32_t sw = (uint32_t)(r_in_tile & 7);
+    const uint32_t s_addr = tmem_s + lane_addr;
+    const uint32_t o_addr = tmem_o + lane_addr;
     uint32_t it_count = 0;  // 64-key blocks processed so far by this CTA
     bool alive = true;
     for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
@@ -280,18 +290,13 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int row = it.q0 + r_in_tile;
       const int warp_row0 = it.q0 + quarter * 32;       // first query row of this warp
       const bool warp_live = warp_row0 < p.L;           // a warp whose 32 rows all lie beyond L only keeps the handshakes going
-      float o[D];
-#pragma unroll
-      for (int i = 0; i < D; ++i) o[i] = 0.f;
-      float m_run = -INFINITY, l_run = 0.f, mult_prev = 0.f;
+      float m_run = -INFINITY, l_run = 0.f;
       for (int j = 0; j < it.nblk; ++j, ++it_count) {
-        const uint32_t sb = it_count & 1;
-        if (!mbar_wait(bar_s_full + 8 * sb, (it_count >> 1) & 1, abort_flag, p.status_word, 18)) {
+        if (!mbar_wait(bar_s_full, it_count & 1, abort_flag, p.status_word, 18)) {
           alive = false;
           break;
         }
         tc_fence_after();
-        const uint32_t s_addr = tmem_s + lane_addr + sb * BLOCK_N;
         const int k0 = j * BLOCK_N;
         // a 32-key chunk whose first key lies above this warp's last row is masked for the whole warp
         const int live_chunks = (!warp_live || k0 > warp_row0 + 31) ? 0 : (k0 + 32 > warp_row0 + 31 ? 1 : 2);
@@ -316,8 +321,10 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const float m_new = fmaxf(m_run, bm * p.scale_log2e);  // running maximum, in log2 units
         const float mult = ex2f(m_run - m_new);
         m_run = m_new;
-        // P buffer must have been consumed by the previous block's P V
-        if (!mbar_wait(bar_p_empty, (it_count & 1) ^ 1u, abort_flag, p.status_word, 19)) {
+        // the previous block's P V must be complete: it read the P tile that is about to be overwritten, and it
+        // produced the O that is about to be rescaled (the first block of an item finds both free: the previous
+        // item's last P V was awaited before its output was stored)
+        if (j > 0 && !mbar_wait(bar_pv_done, (it_count - 1) & 1, abort_flag, p.status_word, 19)) {
           alive = false;
           break;
         }
@@ -365,6 +372,10 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             st_shared_v4(p_row + ((chunk ^ sw) << 4), w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
           }
         }
+        // S has been read: the next block's Q K^T may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_s_empty);
         if constexpr (sizeof(T) == 2 && !IS_FP16) {
           // bf16 storage: V_j -> fp16 in place, 64 bytes per softmax thread (the swizzle is address-agnostic)
           const uint32_t vaddr = smem_kv + (it_count % KV_STAGES) * KV_STAGE_BYTES + KV_TILE_BYTES + (uint32_t)(threadIdx.x - 64) * 64u;
@@ -381,73 +392,55 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             st_shared_v4(vaddr + g * 16, w4[0], w4[1], w4[2], w4[3]);
           }
         }
-        // S[sb] is free; P (and, for bf16, the converted V) is complete
-        tc_fence_before();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar_s_empty + 8 * sb);
-          mbar_arrive(bar_p_full);
-        }
-        l_run = l_run * mult + psum;
-        // fold the previous block's P V:  o = o * mult_prev + PV_{j-1}
-        if (j > 0) {
-          const uint32_t ob = (it_count - 1) & 1;
-          if (!mbar_wait(bar_pv_full + 8 * ob, ((it_count - 1) >> 1) & 1, abort_flag, p.status_word, 20)) {
-            alive = false;
-            break;
-          }
-          tc_fence_after();
-          if (warp_live) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              uint32_t v[32];
-              tmem_ld_32x32(tmem_pv + lane_addr + ob * D + c * 32, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], mult_prev, __uint_as_float(v[i]));
-            }
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_pv_empty + 8 * ob);
-        }
-        mult_prev = mult;
-      }
-      if (!alive) break;
-      // last block's P V, then normalise and store the row
-      {
-        const uint32_t ob = (it_count - 1) & 1;
-        if (!mbar_wait(bar_pv_full + 8 * ob, ((it_count - 1) >> 1) & 1, abort_flag, p.status_word, 21)) break;
-        tc_fence_after();
-        if (warp_live) {
+        // o = o * exp(m_old - m_new) in tensor memory, for this warp's 32 rows, unless no row's maximum moved
+        if (j > 0 && warp_live && __any_sync(0xffffffffu, mult != 1.0f)) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             uint32_t v[32];
-            tmem_ld_32x32(tmem_pv + lane_addr + ob * D + c * 32, v);
+            tmem_ld_32x32(o_addr + c * 32, v);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], mult_prev, __uint_as_float(v[i]));
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * mult);
+            tmem_st_32x32(o_addr + c * 32, v);
           }
+          tmem_st_wait();
         }
+        // P (and, for bf16, the converted V) is complete, O is rescaled: P V of this block may be issued
         tc_fence_before();
+        fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_pv_empty + 8 * ob);
+        if (lane == 0) mbar_arrive(bar_p_full);
+        l_run = l_run * mult + psum;
       }
-      if (row < p.L) {
+      if (!alive) break;
+      // the last block's P V, then normalise and store the row
+      if (!mbar_wait(bar_pv_done, (it_count - 1) & 1, abort_flag, p.status_word, 21)) break;
+      tc_fence_after();
+      if (warp_live) {  // (warp-uniform: the tensor-memory loads below are warp-wide instructions)
         const float inv = 1.0f / l_run;
         T* dst = reinterpret_cast<T*>(p.out) + (int64_t)it.b * p.so_b + (int64_t)it.h * p.so_h + (int64_t)row * p.so_l;
-        uint32_t w[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) w[i] = pack_out<T>(o[2 * i] * inv, o[2 * i + 1] * inv);
-        if (p.out_vec32) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(o_addr + c * 32, v);
+          tmem_ld_wait();
+          uint32_t w[16];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) st_global_v8(dst + g * 16, &w[g * 8]);
-        } else {
+          for (int i = 0; i < 16; ++i) w[i] = pack_out<T>(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
+          if (row < p.L) {
+            if (p.out_vec32) {
+              st_global_v8(dst + c * 32, &w[0]);
+              st_global_v8(dst + c * 32 + 16, &w[8]);
+            } else {
 #pragma unroll
-          for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+              for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+            }
+          }
         }
       }
+      // (this warp's reads of O are ordered before its next arrival on bar_p_full, which is what lets the next
+      // item's first P V overwrite O)
+      tc_fence_before();
     }
   }
 
@@ -471,22 +464,16 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // for views into a fused [B, L, 3*NH*D] projection); *head_inner tells the kernel which order was used.
 static int make_map(CUtensorMap* map, const void* ptr, int64_t B, int64_t NH, int64_t L, const int64_t* s, int box_rows, int dtype,
                     int* head_inner) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return B200_ERR_CUDA;
   *head_inner = s[1] < s[2];
-  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)NH, (cuuint64_t)B};
-  cuuint64_t strides[3] = {(cuuint64_t)s[2] * 2, (cuuint64_t)s[1] * 2, (cuuint64_t)s[0] * 2};
-  cuuint32_t box[4] = {(cuuint32_t)D, (cuuint32_t)box_rows, 1, 1};
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)L, (uint64_t)NH, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)s[2] * 2, (uint64_t)s[1] * 2, (uint64_t)s[0] * 2};
+  uint32_t box[4] = {(uint32_t)D, (uint32_t)box_rows, 1, 1};
   if (*head_inner) {
-    dims[1] = (cuuint64_t)NH, dims[2] = (cuuint64_t)L;
-    strides[0] = (cuuint64_t)s[1] * 2, strides[1] = (cuuint64_t)s[2] * 2;
-    box[1] = 1, box[2] = (cuuint32_t)box_rows;
+    dims[1] = (uint64_t)NH, dims[2] = (uint64_t)L;
+    strides[0] = (uint64_t)s[1] * 2, strides[1] = (uint64_t)s[2] * 2;
+    box[1] = 1, box[2] = (uint32_t)box_rows;
   }
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = fn(map, dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(ptr), dims,
-                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_CUDA;
+  return encode_tensor_map(map, ptr, 4, dims, strides, box, dtype, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
 static bool view_ok(const void* ptr, const int64_t* s, int64_t B, int64_t NH) {
@@ -531,15 +518,15 @@ int launch_attention_sm100(const void* q, const void* k, const void* v, void* ou
   p.out_vec32 = (reinterpret_cast<uintptr_t>(out) & 31) == 0 && os[0] % 16 == 0 && os[1] % 16 == 0 && os[2] % 16 == 0;
   p.status_word = status_word;
   const int64_t n_items = ((L + BLOCK_M - 1) / BLOCK_M) * B * NH;
-  int64_t grid = (int64_t)sm_count() * 2;
+  int64_t grid = (int64_t)sm_count() * CTAS_PER_SM;
   if (grid > n_items) grid = n_items;
   // S = Q K^T in the storage format; P V always fp16 x fp16 (see the top of this file)
-  if (in_dtype == B200_BF16)
-    attention_sm100_kernel<__nv_bfloat16><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p, idesc(1, 1, 0), idesc(0, 0, 1));
-  else
-    attention_sm100_kernel<__half><<<(unsigned)grid, NUM_THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p, idesc(0, 0, 0), idesc(0, 0, 1));
+  LaunchSetup ls(dim3((unsigned)grid), dim3(NUM_THREADS), SMEM_BYTES, stream);
+  const cudaError_t e = in_dtype == B200_BF16
+                            ? cudaLaunchKernelEx(&ls.cfg, attention_sm100_kernel<__nv_bfloat16>, mq, mk, mv, p, idesc(1, 1, 0), idesc(0, 0, 1))
+                            : cudaLaunchKernelEx(&ls.cfg, attention_sm100_kernel<__half>, mq, mk, mv, p, idesc(0, 0, 0), idesc(0, 0, 1));
   note_launches(1);
-  return status_from_cuda(cudaGetLastError());
+  return status_from_cuda(e);
 }
 
 }  // namespace b200

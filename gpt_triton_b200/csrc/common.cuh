@@ -109,6 +109,43 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// ------------------------------------------------------------------ LayerNorm folded into a GEMM: the extension k-block
+// A GEMM that consumes raw rows x with their LayerNorm folded in (rstd * (x W' - mean * colsum(W')) + bias') lets the
+// tensor cores add the two rank-one terms: one extra 64-wide k-block whose A side ("row extension", one per row of
+// x) and B side ("weight extension", one per output column) are laid out so that their dot product is
+//     -mean * colsum + (1 / rstd) * bias',
+// each factor split into a high and a low 16-bit part (v = hi + lo to twice the type's precision) and the four cross
+// products spelled out:
+//     row extension    [-mean_hi, -mean_lo, -mean_hi, -mean_lo,  sd_hi, sd_lo, sd_hi, sd_lo, 0 ...]     sd = 1 / rstd
+//     weight extension [  cs_hi,    cs_hi,    cs_lo,    cs_lo,   b_hi,  b_hi,  b_lo,  b_lo,  0 ...]
+constexpr int kLnExtCols = 64;
+
+template <typename T>
+__device__ __forceinline__ void split_hi_lo(float v, T& hi, T& lo) {
+  hi = from_float<T>(v);
+  lo = from_float<T>(v - to_float(hi));
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(T a, T b) {
+  return (uint32_t)(*reinterpret_cast<const uint16_t*>(&a)) | ((uint32_t)(*reinterpret_cast<const uint16_t*>(&b)) << 16);
+}
+// First 8 elements (16 bytes) of a row extension; the other 56 elements are zero.
+template <typename T>
+__device__ __forceinline__ uint4 ln_ext_head(float mean, float sd) {
+  T mh, ml, sh, sl;
+  split_hi_lo<T>(-mean, mh, ml);
+  split_hi_lo<T>(sd, sh, sl);
+  return make_uint4(pack_pair(mh, ml), pack_pair(mh, ml), pack_pair(sh, sl), pack_pair(sh, sl));
+}
+// First 8 elements of a weight extension.
+template <typename T>
+__device__ __forceinline__ uint4 ln_ext_weight_head(float colsum, float bias) {
+  T ch, cl, bh, bl;
+  split_hi_lo<T>(colsum, ch, cl);
+  split_hi_lo<T>(bias, bh, bl);
+  return make_uint4(pack_pair(ch, ch), pack_pair(cl, cl), pack_pair(bh, bh), pack_pair(bl, bl));
+}
+
 // tanh-form GELU with tanh(y) = 2*sigmoid(2y) - 1, the formulation the reference
 // kernel evaluates (kernels.py:15-26 of the reference project).
 __device__ __forceinline__ float gelu_new(float x) {
@@ -120,8 +157,47 @@ __device__ __forceinline__ float gelu_new(float x) {
   return 0.5f * x * (1.0f + t);
 }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the
+// stream is still running.  pdl_wait() blocks until the predecessor grid has completed and its memory is visible, so
+// what a kernel does before it (barrier set-up, tensor-memory allocation) overlaps the predecessor's tail;
+// pdl_launch_dependents() lets the successor's CTAs be scheduled as soon as SM resources free up.  Both are no-ops in a
+// kernel launched without the attribute.  Every CTA of every kernel that is launched with the attribute calls
+// pdl_wait() before its first access to global memory, on every path, so that "my predecessor has completed" stays
+// transitive along the stream (kernels launched without it are serialised by the stream as usual).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------ launch helpers
 inline int status_from_cuda(cudaError_t e) { return e == cudaSuccess ? B200_OK : B200_ERR_CUDA; }
+
+// Whether kernels are launched with the programmatic-stream-serialization attribute: only when the environment
+// variable B200GPT_PDL=1 (read once) asks for it.  Off by default because it measured slower: in a replayed CUDA graph
+// the kernels of the forward already follow each other within 0.3 us, and letting the next kernel's CTAs take their
+// SMs early cost 2 % at 512 x 300 tokens and 3 % at 64 x 300.
+bool pdl_enabled();
+
+// cudaLaunchConfig_t with room for the two attributes this library uses: cluster size and programmatic serialization.
+struct LaunchSetup {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attrs[2];
+  LaunchSetup(dim3 grid, dim3 block, size_t smem_bytes, cudaStream_t stream, int cluster_x = 1, bool allow_pdl = true) {
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem_bytes, cfg.stream = stream;
+    unsigned n = 0;
+    if (cluster_x > 1) {
+      attrs[n].id = cudaLaunchAttributeClusterDimension;
+      attrs[n].val.clusterDim.x = (unsigned)cluster_x, attrs[n].val.clusterDim.y = 1, attrs[n].val.clusterDim.z = 1;
+      ++n;
+    }
+    if (allow_pdl && pdl_enabled()) {
+      attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attrs[n].val.programmaticStreamSerializationAllowed = 1;
+      ++n;
+    }
+    cfg.attrs = attrs, cfg.numAttrs = n;
+  }
+};
 
 int sm_count();  // cached multiprocessor count of the current device
 // Index of the current device for per-device caches (kernel attributes, occupancy figures); -1 if it cannot be had.
@@ -131,8 +207,18 @@ void note_launches(int n);  // adds to the library-wide count of kernels launche
 uint64_t launches_so_far();
 
 // ------------------------------------------------------------------ internal launchers
+// ln_stats (optional, fp32 pairs [T]): (mean, 1 / sqrt(variance + eps)) of every stored row; ln_ext (with it): the
+// rows' extensions [T, kLnExtCols] in the storage type (16-bit types only)
 int launch_embedding(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t T, int64_t L, int64_t V,
-                     int64_t P, int64_t H, int dtype, int* bad_id_flag, cudaStream_t stream);
+                     int64_t P, int64_t H, int dtype, int* bad_id_flag, float* ln_stats, void* ln_ext, float eps, cudaStream_t stream);
+int launch_row_ln_stats(const void* x, float* ln_stats, void* ln_ext, int64_t M, int64_t H, float eps, int dtype, cudaStream_t stream);
+int launch_fold_layernorm(const void* w, const void* gamma, const void* beta, const void* bias, void* packed, float* colsum, float* bias_out,
+                          void* w_ext, int64_t K, int64_t N, int64_t ld_dst, int dtype, cudaStream_t stream);
+size_t gemm_ln_workspace_bytes(int64_t M, int64_t N);
+int launch_gemm_ln(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                   int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype, int add_gelu, const float* ln_stats,
+                   const void* a_ext, const void* b_ext, float* stats_out, void* ext_out, float eps, void* workspace, size_t workspace_bytes,
+                   int* status_word, cudaStream_t stream);
 int launch_layernorm(const void* x, const void* w, const void* b, void* out, int64_t M, int64_t H, float eps,
                      int in_dtype, int out_dtype, cudaStream_t stream);
 int launch_pack(const void* src, void* dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst, int transpose,

@@ -16,7 +16,9 @@ namespace {
 static __device__ __align__(256) unsigned char g_ffn_scratch[B200_FFN_STATIC_SCRATCH_BYTES];
 
 // In host code `g_ffn_scratch` is only a handle for the runtime, not a device address; the address that
-// kernels may use is obtained once per device, with that device current, from cudaGetSymbolAddress.
+// kernels may use is obtained once per device, with that device current, from cudaGetSymbolAddress.  The
+// cached address belongs to the device's primary context as it was at that first call: after a
+// cudaDeviceReset in this process it is stale, and the entry point must not be called again on that device.
 constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
 void* g_scratch_addr[kMaxDevices] = {};
@@ -35,15 +37,25 @@ int scratch_for_current_device(void** out) {
   return B200_OK;
 }
 
+size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+
 }  // namespace
 
 extern "C" int b200_ffn_static_scratch(const void* x, const void* w, const void* bias, const void* residual, void* out, int64_t M,
                                        int64_t N, int64_t K, int64_t ld_out, int w_is_nk, int add_gelu, int dtype, int* status_word,
                                        void* stream) {
+  if (M < 0 || N < 0 || K < 0) return B200_ERR_BAD_ARGUMENT;
+  if (M == 0 || N == 0) return B200_OK;
+  if (M > 0x7fffffffLL - 256 || N > 0x7fffffffLL - 256 || K > 0x7fffffffLL - 256) return B200_ERR_BAD_ARGUMENT;
+  // What this very call needs, decided the way b200_ffn decides it: an operand is packed into scratch unless it can be
+  // fed to the tensor cores in place (16-bit storage, K a multiple of 8, 16-byte aligned, and for w the [N, K] layout).
   // Refuse, before anything is launched, a problem whose packed operands do not fit the built-in array.
-  // The figure is the worst case (both operands packed), so it does not depend on pointer alignment.
-  const size_t worst_case = b200_ffn_workspace_bytes(M, N, K, 0, B200_F32);
-  if (worst_case > (size_t)B200_FFN_STATIC_SCRATCH_BYTES) return B200_ERR_WORKSPACE;
+  const bool in_place_ok = dtype != B200_F32 && K % 8 == 0;
+  const size_t kp = (size_t)((K + 7) / 8 * 8);
+  size_t need = 0;
+  if (!(in_place_ok && (reinterpret_cast<uintptr_t>(x) & 15) == 0)) need += round256((size_t)M * kp * 2);
+  if (!(w_is_nk && in_place_ok && (reinterpret_cast<uintptr_t>(w) & 15) == 0)) need += round256((size_t)N * kp * 2);
+  if (need > (size_t)B200_FFN_STATIC_SCRATCH_BYTES) return B200_ERR_WORKSPACE;
   void* scratch = nullptr;
   const int st = scratch_for_current_device(&scratch);
   if (st != B200_OK) return st;

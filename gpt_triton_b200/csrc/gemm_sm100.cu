@@ -55,6 +55,7 @@ constexpr int EPI_BOX_COLS = 64;        // TMA store box: 64 columns (128 bytes 
 constexpr int EPI_BOX_BYTES = 32 * EPI_BOX_COLS * 2;        // 4 KB
 constexpr int EPI_WARP_STAGE_BYTES = (EPI_COLS / EPI_BOX_COLS) * EPI_BOX_BYTES;  // one box per 64 of the warp's 128 columns: 8 KB
 constexpr int EPI_STAGE_BYTES = NUM_EPI_WARPS * EPI_WARP_STAGE_BYTES;
+static_assert(kLnExtCols == BK, "the LayerNorm extension is exactly one k-block");
 
 template <int CTAS>
 struct Cfg {
@@ -147,6 +148,22 @@ struct EpilogueArgs {
   // Output is written once and not read back soon, and B is large: store it with evict-first priority so that it
   // does not push B out of L2 (the tied lm_head: 77 MB of B against gigabytes of logits).
   int stream_out;
+  // LN == 1, a LayerNorm folded into this GEMM: A holds the raw rows x, B the weights already multiplied by the
+  // LayerNorm weight, and one extra 64-wide k-block comes from the two "extension" matrices (see launch_gemm_ln): its
+  // products add  -mean_row * colsum[col] + (1 / rstd_row) * ln_bias[col]  to the accumulator, so that all the
+  // epilogue has left to do is  out = rstd_row * acc  (then GELU / residual as usual).  No bias vector is read.
+  const float2* ln_stats;  // per row of A: (mean, rstd)
+  // LN == 2, the producer side: per row and per EPI_COLS-column slice of the output, the (mean, centred sum of
+  // squares) of the values this epilogue stores, slice-major: stats_out[slice * stats_out_ld + row].  A small second
+  // kernel merges a row's slices into its (mean, rstd).
+  float2* stats_out;
+  int64_t stats_out_ld;
+};
+
+// Shifted sums of one thread's part of an output row (LN == 2): sum and sum of squares of (value - shift), the shift
+// being the first value seen, so that the centred sum of squares comes out without cancellation.
+struct SliceMoments {
+  float shift, s1, s2, n;
 };
 
 // x * sigmoid(2y), y = sqrt(2/pi) (x + 0.044715 x^3): algebraically the reference's
@@ -289,14 +306,22 @@ struct ResidualRegs {
 // `bias_s` points at this chunk's 32 fp32 bias values in shared memory (zeros when there is no bias).
 // With `stage` != 0 (TMA-store path, 16-bit output) the 64 result bytes go to this thread's row of the warp's
 // staging tile at 16-byte slots [4*half, 4*half+4) (128-byte swizzle); otherwise they are stored to global memory.
-template <typename OutT, bool GELU, int STATS>
+template <typename OutT, bool GELU, int STATS, int LN>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const float* bias_s, const EpilogueArgs<OutT>& e,
                                                const uint4* res_regs, int64_t row, int col0, int64_t N, int mode, uint32_t stage,
-                                               int half, int lane, bool row_ok, bool res_staged, RowStats& st) {
+                                               int half, int lane, bool row_ok, bool res_staged, RowStats& st, float ln_r, SliceMoments& mom) {
   // Two columns per instruction where the hardware has packed fp32 forms (add, mul, fma: same roundings as the
   // scalar ones); no bias, no add.
   float f[32];
-  if (e.bias) {
+  if constexpr (LN == 1) {
+    // folded LayerNorm: the extension k-block already put -mean * colsum + ln_bias / rstd into the accumulator
+    const float2 r2 = make_float2(ln_r, ln_r);
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const float2 v2 = __fmul2_rn(make_float2(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1])), r2);
+      f[j] = v2.x, f[j + 1] = v2.y;
+    }
+  } else if (e.bias) {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
       const float4 b = *reinterpret_cast<const float4*>(bias_s + j);
@@ -355,6 +380,29 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
 #pragma unroll
         for (int j = 0; j < 32; ++j)
           if (col0 + j < N) f[j] += to_float(rrow[j]);
+      }
+      if constexpr (LN == 2) {
+        // moments of this row's slice, over the fp32 values about to be rounded and stored
+        if (mom.n == 0.f) mom.shift = f[0];
+        const float2 sh = make_float2(-mom.shift, -mom.shift);
+        if (full) {
+          float2 a1 = make_float2(0.f, 0.f), a2 = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float2 d = __fadd2_rn(make_float2(f[j], f[j + 1]), sh);
+            a1 = __fadd2_rn(a1, d);
+            a2 = __ffma2_rn(d, d, a2);
+          }
+          mom.s1 += a1.x + a1.y, mom.s2 += a2.x + a2.y, mom.n += 32.f;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + j < N) {
+              const float d = f[j] - mom.shift;
+              mom.s1 += d, mom.s2 = fmaf(d, d, mom.s2), mom.n += 1.f;
+            }
+          }
+        }
       }
       uint32_t w[16];
 #pragma unroll
@@ -534,10 +582,13 @@ __device__ __forceinline__ void stats_only_chunk(const uint32_t (&acc)[32], cons
   }
 }
 
-template <typename OutT, bool GELU, int CTAS, int STATS>
+// LN: 0 = plain; 1 = a LayerNorm of A's rows is folded into the epilogue (EpilogueArgs::ln_*); 2 = the epilogue also
+// emits per-slice row moments of what it stores (EpilogueArgs::stats_out), which a following LN == 1 GEMM consumes.
+template <typename OutT, bool GELU, int CTAS, int STATS, int LN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res, EpilogueArgs<OutT> epi,
+               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_res,
+               const __grid_constant__ CUtensorMap map_a_ext, const __grid_constant__ CUtensorMap map_b_ext, EpilogueArgs<OutT> epi,
                int64_t M, int64_t N, int64_t K, uint32_t idesc, int panel_n, int* status_word) {
   using C = Cfg<CTAS>;
   constexpr int STAGES = C::STAGES;
@@ -546,6 +597,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);
   if (base & 1023u) {  // never expected; refuse to run rather than compute on misplaced tiles (uniform over the grid)
+    pdl_wait();
     if (threadIdx.x == 0 && status_word) atomicCAS(status_word, 0, 99);
     return;
   }
@@ -575,7 +627,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int m_tiles = (int)((M + C::TILE_M - 1) / C::TILE_M);
   const int n_tiles = (int)((N + BN - 1) / BN);
   const int64_t num_tiles = (int64_t)m_tiles * n_tiles;
-  const int num_kb = (int)((K + BK - 1) / BK);
+  const int num_kb_ab = (int)((K + BK - 1) / BK);
+  const int num_kb = num_kb_ab + (LN == 1 ? 1 : 0);  // a folded LayerNorm appends the extension k-block
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -606,6 +659,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if constexpr (CTAS == 2) cluster_sync_all();  // both CTAs' barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only this CTA's own shared and tensor memory and may overlap the previous kernel of the
+  // stream; from here on global memory is read and written.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -624,14 +681,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             alive = false;
             break;
           }
+          // (LN == 1: the last k-block is the 64-wide extension pair, at column 0 of its own two matrices)
+          const bool ext = LN == 1 && kb == num_kb_ab;
+          const CUtensorMap* ma = ext ? &map_a_ext : &map_a;
+          const CUtensorMap* mb = ext ? &map_b_ext : &map_b;
+          const int kcol = ext ? 0 : kb * BK;
           if constexpr (CTAS == 2) {
             if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);
-            tma_load_2d_pair(smem_a + stage * C::A_STAGE_BYTES, &map_a, full_base + 8 * stage, kb * BK, row_a);
-            tma_load_2d_pair(smem_b + stage * C::B_STAGE_BYTES, &map_b, full_base + 8 * stage, kb * BK, row_b);
+            tma_load_2d_pair(smem_a + stage * C::A_STAGE_BYTES, ma, full_base + 8 * stage, kcol, row_a);
+            tma_load_2d_pair(smem_b + stage * C::B_STAGE_BYTES, mb, full_base + 8 * stage, kcol, row_b);
           } else {
             mbar_arrive_expect_tx(bar_full + 8 * stage, C::STAGE_BYTES);
-            tma_load_2d(smem_a + stage * C::A_STAGE_BYTES, &map_a, bar_full + 8 * stage, kb * BK, row_a);
-            tma_load_2d(smem_b + stage * C::B_STAGE_BYTES, &map_b, bar_full + 8 * stage, kb * BK, row_b);
+            tma_load_2d(smem_a + stage * C::A_STAGE_BYTES, ma, bar_full + 8 * stage, kcol, row_a);
+            tma_load_2d(smem_b + stage * C::B_STAGE_BYTES, mb, bar_full + 8 * stage, kcol, row_b);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -726,8 +788,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       float* bias_s = bias_smem + acc * BN;
       for (int i = epi_tid; i < BN; i += 32 * NUM_EPI_WARPS) {
         const int c = tc.n * BN + i;
-        bias_s[i] = (epi.bias && c < N) ? to_float(epi.bias[c]) : 0.f;
+        if constexpr (LN != 1) bias_s[i] = (epi.bias && c < N) ? to_float(epi.bias[c]) : 0.f;
       }
+      // folded LayerNorm: this row's rstd
+      float ln_r = 1.f;
+      if constexpr (LN == 1) {
+        if (row_ok) ln_r = __ldg(epi.ln_stats + row).y;
+      }
+      SliceMoments mom{0.f, 0.f, 0.f, 0.f};
       ResidualRegs res;
       const bool res_in_regs = !use_tma && esz == 2 && epi.residual && mode != STORE_SCALAR && row_ok;
       if (res_in_regs) {
@@ -738,9 +806,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       // bias visible to all epilogue warps (an mbarrier, not bar.sync: its wait is bounded like every other)
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_bias + 8 * acc);
-      if (!mbar_wait(bar_bias + 8 * acc, acc_phase, abort_flag, status_word, 5)) break;
+      if constexpr (LN != 1) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_bias + 8 * acc);
+        if (!mbar_wait(bar_bias + 8 * acc, acc_phase, abort_flag, status_word, 5)) break;
+      }
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, status_word, 4)) break;
       if (res_tma) {
         if (!mbar_wait(my_res_bar, res_phase, abort_flag, status_word, 6)) break;
@@ -785,8 +855,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
           }
           if (col0 < N)
-            epilogue_chunk<OutT, GELU, STATS>(v, bias_s + col_half * EPI_COLS + c * 32, epi, nullptr, row, col0, N, mode, box, c & 1, lane, row_ok,
-                                       res_tma, stats);
+            epilogue_chunk<OutT, GELU, STATS, LN>(v, bias_s + col_half * EPI_COLS + c * 32, epi, nullptr, row, col0, N, mode, box, c & 1, lane, row_ok,
+                                                  res_tma, stats, ln_r, mom);
           if ((c & 1) == 1) {
             fence_proxy_async_smem();
             __syncwarp();
@@ -800,8 +870,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         } else if (row_ok && col0 < N) {
-          epilogue_chunk<OutT, GELU, STATS>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N, mode, 0u,
-                                     0, lane, row_ok, false, stats);
+          epilogue_chunk<OutT, GELU, STATS, LN>(v, bias_s + col_half * EPI_COLS + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res.v[c * 4] : nullptr, row, col0, N,
+                                                mode, 0u, 0, lane, row_ok, false, stats, ln_r, mom);
         }
       }
       if constexpr (STATS != 0 && sizeof(OutT) == 2) {
@@ -810,6 +880,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int c = (stats.pending_col0 - col_base) >> 5;
           stats.best_idx = stats.pending_col0 + find_staged_column<OutT>((STATS == 3 ? stats_stage : stage_addr) + (uint32_t)(c >> 1) * EPI_BOX_BYTES,
                                                                          c & 1, lane, stats.best_val);
+        }
+      }
+      if constexpr (LN == 2) {
+        if (row_ok && mom.n > 0.f) {
+          // (mean, centred sum of squares) of this row's slice
+          const float inv = 1.0f / mom.n;
+          const int64_t slice = (int64_t)tc.n * (BN / EPI_COLS) + col_half;
+          epi.stats_out[slice * epi.stats_out_ld + row] = make_float2(fmaf(mom.s1, inv, mom.shift), fmaxf(mom.s2 - mom.s1 * mom.s1 * inv, 0.f));
         }
       }
       if (STATS && row_ok) {
@@ -847,42 +925,27 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ------------------------------------------------------------------ host side
 // 2-D map over a row-major [rows, cols] 16-bit matrix with leading dimension ld; box = 64 columns x box_rows.
 static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows, int op_dtype) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return B200_ERR_CUDA;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, op_dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_CUDA;
+  const uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows}, strides[1] = {(uint64_t)ld * 2};
+  const uint32_t box[2] = {(uint32_t)BK, (uint32_t)box_rows};
+  return encode_tensor_map(map, ptr, 2, dims, strides, box, op_dtype, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
 // Largest number of 2-CTA clusters of this kernel that can be resident at once (cached per instantiation).
-template <typename OutT, bool GELU, int STATS>
+template <typename OutT, bool GELU, int STATS, int LN>
 static int max_pairs() {
   static std::atomic<int> cache[kMaxDevices];  // per device; stored as value + 1 so that 0 means "not asked yet"
   const int slot = device_slot();
   if (slot < 0) return 0;
   const int seen = cache[slot].load(std::memory_order_acquire);
   if (seen > 0) return seen - 1;
-  if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, 2, STATS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES) != cudaSuccess) {
+  if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, 2, STATS, LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES) != cudaSuccess) {
     cudaGetLastError();
     cache[slot].store(1, std::memory_order_release);
     return 0;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)sm_count() / 2 * 2);
-  cfg.blockDim = dim3(NUM_THREADS);
-  cfg.dynamicSmemBytes = Cfg<2>::SMEM_BYTES;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  LaunchSetup ls(dim3((unsigned)sm_count() / 2 * 2), dim3(NUM_THREADS), Cfg<2>::SMEM_BYTES, nullptr, 2, false);
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_tn_kernel<OutT, GELU, 2, STATS>, &cfg) != cudaSuccess || n < 1) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tn_kernel<OutT, GELU, 2, STATS, LN>, &ls.cfg) != cudaSuccess || n < 1) {
     cudaGetLastError();
     n = 0;
   }
@@ -892,53 +955,49 @@ static int max_pairs() {
 
 // Map over a 16-bit [M, N] matrix (pitch ld) for tile stores/loads of 64 columns x 32 rows (output, residual).
 static int make_out_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N, int64_t ld_out, int io_dtype) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return B200_ERR_CUDA;
-  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-  cuuint64_t strides[1] = {(cuuint64_t)ld_out * 2};
-  cuuint32_t box[2] = {(cuuint32_t)EPI_BOX_COLS, 32};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, io_dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ptr, dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_CUDA;
+  const uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[1] = {(uint64_t)ld_out * 2};
+  const uint32_t box[2] = {(uint32_t)EPI_BOX_COLS, 32};
+  return encode_tensor_map(map, ptr, 2, dims, strides, box, io_dtype, CU_TENSOR_MAP_L2_PROMOTION_NONE);
 }
 
-template <typename OutT, bool GELU, int CTAS, int STATS>
-static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mr, const EpilogueArgs<OutT>& epi, int64_t M, int64_t N, int64_t K,
-                          int op_dtype, int64_t groups, int* status_word, cudaStream_t stream) {
+template <typename OutT, bool GELU, int CTAS, int STATS, int LN>
+static int launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mr, const CUtensorMap& mae,
+                          const CUtensorMap& mbe, const EpilogueArgs<OutT>& epi, int64_t M, int64_t N, int64_t K, int op_dtype, int64_t groups,
+                          int* status_word, cudaStream_t stream) {
   using C = Cfg<CTAS>;
   static std::atomic<bool> attr_set[kMaxDevices];  // kernel attributes are per device
   const int slot = device_slot();
   if (slot < 0) return B200_ERR_CUDA;
   if (!attr_set[slot].load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, CTAS, STATS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_tn_kernel<OutT, GELU, CTAS, STATS, LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
       return B200_ERR_CUDA;
     attr_set[slot].store(true, std::memory_order_release);
   }
   const uint32_t idesc = make_idesc(op_dtype == B200_BF16 ? 1 : 0, BM * CTAS);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(groups * CTAS));
-  cfg.blockDim = dim3(NUM_THREADS);
-  cfg.dynamicSmemBytes = C::SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = CTAS, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  LaunchSetup ls(dim3((unsigned)(groups * CTAS)), dim3(NUM_THREADS), C::SMEM_BYTES, stream, CTAS);
   // column panel: about 16 MB of B (panel_n * 256 rows of K 16-bit elements), at least 8 tiles
   int panel_n = (int)(16e6 / ((double)BN * (double)K * 2.0));
   if (panel_n < 8) panel_n = 8;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tn_kernel<OutT, GELU, CTAS, STATS>, ma, mb, mo, mr, epi, M, N, K, idesc, panel_n, status_word);
+  cudaError_t e = cudaLaunchKernelEx(&ls.cfg, gemm_tn_kernel<OutT, GELU, CTAS, STATS, LN>, ma, mb, mo, mr, mae, mbe, epi, M, N, K, idesc, panel_n, status_word);
   note_launches(1);
   return status_from_cuda(e);
 }
 
-template <typename OutT, bool GELU, int STATS>
+// What a LayerNorm-aware launch adds to the plain arguments (see EpilogueArgs).
+struct LnArgs {
+  const float2* stats = nullptr;  // consumer: (mean, rstd) of A's rows
+  const void* a_ext = nullptr;    // consumer: [M, kLnExtCols] row extension (write_ln_ext), 16-bit of the operand type
+  const void* b_ext = nullptr;    // consumer: [N, kLnExtCols] weight extension (fold_layernorm_kernel)
+  float2* stats_out = nullptr;  // producer: per-slice row moments of the output
+  int64_t stats_out_ld = 0;
+};
+
+template <typename OutT, bool GELU, int STATS, int LN = 0>
 static int launch_typed(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K,
                         int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, const ArgmaxPartials& am, int* status_word,
-                        cudaStream_t stream, const int64_t* targets = nullptr, float* target_val = nullptr) {
-  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.sum, am.ld, targets, target_val, 0};
+                        cudaStream_t stream, const int64_t* targets = nullptr, float* target_val = nullptr, const LnArgs& ln = LnArgs()) {
+  EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.sum, am.ld, targets, target_val, 0,
+                         ln.stats, ln.stats_out, ln.stats_out_ld};
   CUtensorMap mo, mr;
   memset(&mo, 0, sizeof(mo));
   memset(&mr, 0, sizeof(mr));
@@ -948,23 +1007,32 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
       make_out_map(&mo, out, M, N, ld_out, DType<OutT>::code) == B200_OK &&
       (!residual || make_out_map(&mr, const_cast<void*>(residual), M, N, ld_res, DType<OutT>::code) == B200_OK))
     epi.tma_store = 1;
+  if (LN != 0 && !epi.tma_store) return B200_ERR_UNSUPPORTED;  // the LayerNorm-aware epilogues exist on the staged 16-bit path only
   epi.stream_out = epi.tma_store && (double)N * (double)K * 2.0 >= 32e6 && (double)M * (double)N * sizeof(OutT) >= 512e6;
   const int64_t n_tiles = (N + BN - 1) / BN;
-  const int pairs = M > BM ? max_pairs<OutT, GELU, STATS>() : 0;
-  CUtensorMap ma, mb;
+  const int pairs = M > BM ? max_pairs<OutT, GELU, STATS, LN>() : 0;
+  CUtensorMap ma, mb, mae, mbe;
+  memset(&mae, 0, sizeof(mae));
+  memset(&mbe, 0, sizeof(mbe));
   int st = make_map(&ma, a, M, K, lda, BM, op_dtype);
   if (st != B200_OK) return st;
+  if (LN == 1) {
+    st = make_map(&mae, ln.a_ext, M, kLnExtCols, kLnExtCols, BM, op_dtype);
+    if (st != B200_OK) return st;
+  }
   if (pairs > 0) {
     st = make_map(&mb, b, N, K, ldb, Cfg<2>::B_ROWS, op_dtype);
+    if (st == B200_OK && LN == 1) st = make_map(&mbe, ln.b_ext, N, kLnExtCols, kLnExtCols, Cfg<2>::B_ROWS, op_dtype);
     if (st != B200_OK) return st;
     const int64_t tiles = ((M + Cfg<2>::TILE_M - 1) / Cfg<2>::TILE_M) * n_tiles;
-    return launch_variant<OutT, GELU, 2, STATS>(ma, mb, mo, mr, epi, M, N, K, op_dtype, tiles < pairs ? tiles : pairs, status_word, stream);
+    return launch_variant<OutT, GELU, 2, STATS, LN>(ma, mb, mo, mr, mae, mbe, epi, M, N, K, op_dtype, tiles < pairs ? tiles : pairs, status_word, stream);
   }
   st = make_map(&mb, b, N, K, ldb, Cfg<1>::B_ROWS, op_dtype);
+  if (st == B200_OK && LN == 1) st = make_map(&mbe, ln.b_ext, N, kLnExtCols, kLnExtCols, Cfg<1>::B_ROWS, op_dtype);
   if (st != B200_OK) return st;
   const int64_t tiles = ((M + BM - 1) / BM) * n_tiles;
   const int64_t sms = sm_count();
-  return launch_variant<OutT, GELU, 1, STATS>(ma, mb, mo, mr, epi, M, N, K, op_dtype, tiles < sms ? tiles : sms, status_word, stream);
+  return launch_variant<OutT, GELU, 1, STATS, LN>(ma, mb, mo, mr, mae, mbe, epi, M, N, K, op_dtype, tiles < sms ? tiles : sms, status_word, stream);
 }
 
 }  // namespace gemm
@@ -982,6 +1050,8 @@ argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx,
   __shared__ float s_sum[kReduceSplit][kReduceRows];
   const int x = threadIdx.x & (kReduceRows - 1), y = threadIdx.x / kReduceRows;
   const int64_t row = (int64_t)blockIdx.x * kReduceRows + x;
+  pdl_launch_dependents();
+  pdl_wait();
   float best = -INFINITY, total = 0.f;
   int where = 0x7fffffff;
   if (row < M) {
@@ -1012,6 +1082,111 @@ argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx,
     out[row] = where == 0x7fffffff ? 0 : where;
     if (lse_out) lse_out[row] = best + logf(total);
   }
+}
+
+static int launch_argmax_reduce(const float* val, const int* idx, const float* sum, int64_t ld, int slices, int64_t M, int64_t* out, float* lse_out,
+                                cudaStream_t stream) {
+  LaunchSetup ls(dim3((unsigned)((M + kReduceRows - 1) / kReduceRows)), dim3(kReduceRows * kReduceSplit), 0, stream);
+  const cudaError_t e = cudaLaunchKernelEx(&ls.cfg, argmax_reduce_kernel, val, idx, sum, ld, slices, M, out, lse_out);
+  note_launches(1);
+  return status_from_cuda(e);
+}
+
+// Merges the per-slice (mean, centred sum of squares) pairs a LN == 2 epilogue wrote into one (mean, rstd) per row:
+// mean = sum_s n_s mean_s / n,  M2 = sum_s M2_s + sum_s n_s (mean_s - mean)^2  (every term non-negative: no
+// cancellation),  rstd = 1 / sqrt(M2 / n + eps); also writes the row's extension for a consuming GEMM.  One thread per
+// row; the slices of 32 consecutive rows are consecutive in memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ln_stats_from_moments_kernel(const float2* __restrict__ moments, int64_t ld, int slices, int slice_cols, int cols, float eps, int64_t M,
+                             float2* __restrict__ stats, T* __restrict__ ext) {
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (row >= M) return;
+  float wsum = 0.f;
+  for (int s = 0; s < slices; ++s) wsum = fmaf((float)min(slice_cols, cols - s * slice_cols), moments[(int64_t)s * ld + row].x, wsum);
+  const float mean = wsum / (float)cols;
+  float m2 = 0.f;
+  for (int s = 0; s < slices; ++s) {
+    const float2 part = moments[(int64_t)s * ld + row];
+    const float d = part.x - mean;
+    m2 += fmaf((float)min(slice_cols, cols - s * slice_cols) * d, d, part.y);
+  }
+  const float sd = sqrtf(m2 / (float)cols + eps);
+  stats[row] = make_float2(mean, 1.0f / sd);
+  if (ext) {
+    uint4* dst = reinterpret_cast<uint4*>(ext + row * kLnExtCols);
+    dst[0] = ln_ext_head<T>(mean, sd);
+#pragma unroll
+    for (int i = 1; i < kLnExtCols * 2 / 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+size_t gemm_ln_workspace_bytes(int64_t M, int64_t N) {
+  if (M <= 0 || N <= 0) return 0;
+  const int64_t slices = (N + gemm::EPI_COLS - 1) / gemm::EPI_COLS;
+  return (size_t)(slices * ((M + 63) / 64 * 64)) * 8;
+}
+
+// GEMM with a LayerNorm on either side of it (16-bit data, staged epilogue only):
+//  * consumer (ln_stats != NULL): A holds raw rows x whose LayerNorm is folded into this GEMM: ln_stats[row] =
+//    (mean, rstd) of x's rows and a_ext [M, kLnExtCols] their extension (both written by one of the statistics
+//    producers), B holds the weights already multiplied by the LayerNorm weight and b_ext [N, kLnExtCols] their
+//    extension (both written by fold_layernorm_kernel); `bias` is not used (it is inside b_ext);
+//  * producer (stats_out != NULL): plain GEMM that also leaves stats_out[row] = (mean, rstd over N columns, with eps)
+//    and ext_out [M, kLnExtCols] of the rows it stores, for a following consumer; `workspace`
+//    (gemm_ln_workspace_bytes) holds the per-slice moments.
+int launch_gemm_ln(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                   int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype, int add_gelu, const float* ln_stats,
+                   const void* a_ext, const void* b_ext, float* stats_out, void* ext_out, float eps, void* workspace, size_t workspace_bytes,
+                   int* status_word, cudaStream_t stream) {
+  using namespace gemm;
+  if (M == 0 || N == 0) return B200_OK;
+  if (K < 1 || M < 0 || N < 0) return B200_ERR_BAD_ARGUMENT;
+  if (op_dtype != B200_F16 && op_dtype != B200_BF16) return B200_ERR_BAD_ARGUMENT;
+  if (io_dtype != B200_F16 && io_dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
+  if (!a || !b || !out) return B200_ERR_BAD_ARGUMENT;
+  if ((ln_stats != nullptr) == (stats_out != nullptr)) return B200_ERR_BAD_ARGUMENT;  // exactly one of the two roles per launch
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || lda % 8 || ldb % 8 || lda < K || ldb < K)
+    return B200_ERR_ALIGNMENT;
+  if (ld_out < N || (residual && ld_res < N)) return B200_ERR_BAD_ARGUMENT;
+  if (M > 0x7fffffffLL - 256 || N > 0x7fffffffLL - 256 || K > 0x7fffffffLL - 64) return B200_ERR_BAD_ARGUMENT;
+  LnArgs ln;
+  if (op_dtype != io_dtype) return B200_ERR_UNSUPPORTED;  // the extensions are written in the storage type and fed to the tensor cores as they are
+  if (ln_stats) {
+    if (!a_ext || !b_ext || (reinterpret_cast<uintptr_t>(ln_stats) & 7) || (reinterpret_cast<uintptr_t>(a_ext) & 15) ||
+        (reinterpret_cast<uintptr_t>(b_ext) & 15))
+      return B200_ERR_BAD_ARGUMENT;
+    ln.stats = reinterpret_cast<const float2*>(ln_stats), ln.a_ext = a_ext, ln.b_ext = b_ext;
+  } else {
+    if (add_gelu || !ext_out || (reinterpret_cast<uintptr_t>(stats_out) & 7) || (reinterpret_cast<uintptr_t>(ext_out) & 15)) return B200_ERR_BAD_ARGUMENT;
+    if (!workspace || workspace_bytes < gemm_ln_workspace_bytes(M, N) || (reinterpret_cast<uintptr_t>(workspace) & 15)) return B200_ERR_WORKSPACE;
+    ln.stats_out = reinterpret_cast<float2*>(workspace), ln.stats_out_ld = (M + 63) / 64 * 64;
+  }
+  const ArgmaxPartials none{nullptr, nullptr, nullptr, 0};
+  int st;
+#define B200_GEMM_LN_DISPATCH(T)                                                                                                                 \
+  st = ln_stats ? (add_gelu ? launch_typed<T, true, 0, 1>(a, b, nullptr, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, none, status_word, \
+                                                          stream, nullptr, nullptr, ln)                                                          \
+                            : launch_typed<T, false, 0, 1>(a, b, nullptr, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, none, status_word, \
+                                                           stream, nullptr, nullptr, ln))                                                        \
+                : launch_typed<T, false, 0, 2>(a, b, bias, residual, out, M, N, K, lda, ldb, ld_res, ld_out, op_dtype, none, status_word, stream, \
+                                               nullptr, nullptr, ln)
+  if (io_dtype == B200_F16) B200_GEMM_LN_DISPATCH(__half);
+  else B200_GEMM_LN_DISPATCH(__nv_bfloat16);
+#undef B200_GEMM_LN_DISPATCH
+  if (st != B200_OK || !stats_out) return st;
+  const int slices = (int)((N + EPI_COLS - 1) / EPI_COLS);
+  LaunchSetup ls(dim3((unsigned)((M + 255) / 256)), dim3(256), 0, stream);
+  const cudaError_t e =
+      io_dtype == B200_F16
+          ? cudaLaunchKernelEx(&ls.cfg, ln_stats_from_moments_kernel<__half>, (const float2*)ln.stats_out, ln.stats_out_ld, slices, (int)EPI_COLS,
+                               (int)N, eps, M, reinterpret_cast<float2*>(stats_out), static_cast<__half*>(ext_out))
+          : cudaLaunchKernelEx(&ls.cfg, ln_stats_from_moments_kernel<__nv_bfloat16>, (const float2*)ln.stats_out, ln.stats_out_ld, slices,
+                               (int)EPI_COLS, (int)N, eps, M, reinterpret_cast<float2*>(stats_out), static_cast<__nv_bfloat16*>(ext_out));
+  note_launches(1);
+  return status_from_cuda(e);
 }
 
 int launch_gemm(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
@@ -1066,9 +1241,7 @@ int launch_gemm_argmax(const void* a, const void* b, const void* bias, const voi
 #undef B200_GEMM_DISPATCH
   if (st != B200_OK || !argmax_out) return st;
   const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
-  argmax_reduce_kernel<<<(unsigned)((M + kReduceRows - 1) / kReduceRows), kReduceRows * kReduceSplit, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
-  note_launches(1);
-  return status_from_cuda(cudaGetLastError());
+  return launch_argmax_reduce(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out, stream);
 }
 
 // Row statistics of A B^T (+ bias) without storing the product: argmax, log-sum-exp and, optionally, the value at a
@@ -1100,9 +1273,7 @@ int launch_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t
   else
     st = launch_typed<__nv_bfloat16, false, 3>(a, b, bias, nullptr, nullptr, M, N, K, lda, ldb, 0, N, op_dtype, am, status_word, stream, targets, target_out);
   if (st != B200_OK) return st;
-  argmax_reduce_kernel<<<(unsigned)((M + kReduceRows - 1) / kReduceRows), kReduceRows * kReduceSplit, 0, stream>>>(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out);
-  note_launches(1);
-  return status_from_cuda(cudaGetLastError());
+  return launch_argmax_reduce(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out, stream);
 }
 
 }  // namespace b200

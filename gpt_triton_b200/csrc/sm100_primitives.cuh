@@ -3,8 +3,10 @@
 #pragma once
 
 #include <cuda.h>
+#include <string.h>
 
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -177,6 +179,61 @@ inline EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Tiled tensor map over 16-bit data, 128-byte swizzle, no interleave, zero fill: the only kind this library uses.
+// Encoding one costs the host about a microsecond and a forward pass asks for the same few hundred maps again and
+// again, so encoded maps are kept in a process-wide table keyed by everything that goes into the encoding (base
+// pointer, extents, byte strides, box, element type, L2 promotion).  A map owns nothing: an entry stays correct for
+// as long as the same address holds a tensor of the same geometry, whoever allocated it.
+struct TensorMapKey {
+  const void* ptr;
+  uint64_t dims[4], strides[3];
+  uint32_t box[4];
+  int rank, dtype, promotion, reserved;  // (reserved keeps the struct free of padding: it is compared bytewise)
+  bool operator==(const TensorMapKey& o) const { return memcmp(this, &o, sizeof(TensorMapKey)) == 0; }
+};
+struct TensorMapKeyHash {
+  size_t operator()(const TensorMapKey& k) const {
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    uint64_t h = 0x9E3779B97F4A7C15ull;
+    for (size_t i = 0; i < sizeof(TensorMapKey) / 8; ++i) h = (h ^ w[i]) * 0x100000001B3ull + (h >> 29);
+    return (size_t)h;
+  }
+};
+static_assert(sizeof(TensorMapKey) == 8 + 32 + 24 + 16 + 16, "the key is hashed and compared as 64-bit words and must have no padding");
+
+// dims/strides/box as cuTensorMapEncodeTiled takes them (innermost first; strides in bytes for dimensions 1..rank-1).
+inline int encode_tensor_map(CUtensorMap* out, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+                             int dtype, CUtensorMapL2promotion promotion) {
+  TensorMapKey key;
+  memset(&key, 0, sizeof(key));
+  key.ptr = ptr, key.rank = rank, key.dtype = dtype, key.promotion = (int)promotion;
+  for (int i = 0; i < rank; ++i) key.dims[i] = dims[i], key.box[i] = box[i];
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides[i];
+  static std::mutex mutex;
+  static std::unordered_map<TensorMapKey, CUtensorMap, TensorMapKeyHash> table;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    auto it = table.find(key);
+    if (it != table.end()) {
+      *out = it->second;
+      return B200_OK;
+    }
+  }
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return B200_ERR_CUDA;
+  cuuint64_t d[4], st[3];
+  cuuint32_t bx[4], estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) d[i] = dims[i], bx[i] = box[i];
+  for (int i = 0; i + 1 < rank; ++i) st[i] = strides[i];
+  const CUresult r = fn(out, dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
+                        const_cast<void*>(ptr), d, st, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promotion,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return B200_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (table.size() >= 16384) table.clear();  // bounded: a long-lived process with ever-changing shapes starts over
+  table.emplace(key, *out);
+  return B200_OK;
+}
 
 }  // namespace sm100
 }  // namespace b200

@@ -9,6 +9,11 @@ state dict loads unchanged (gpt.py:199-247).  What is new:
   ``FusedGPT.lm_head`` add the tied head that the reference leaves commented out
   (gpt.py:159-161, 172-179) and use ``wte`` itself as a K-major operand, not its transpose;
 * every GEMM weight is packed once per parameter version into the tensor-core operand layout;
+* in 16-bit models ``FusedGPT.forward`` folds the two LayerNorms of every block into the GEMMs that follow them
+  (the fusion the reference leaves as a TODO, kernels.py:132-133): row statistics come out of the kernel that wrote
+  the rows (embedding, c_proj, ffn2), the normalised activations are never written, and 24 of the 25 LayerNorm
+  launches of a 12-layer forward disappear.  ``FusedGPT.fold_layer_norm = False`` (or calling a block module on its
+  own) gives the operator-by-operator sequence of the reference; the two differ by roundings only;
 * attention reads q/k/v as views of the c_attn output and writes merged heads, so the four
   per-layer copies of the reference (kernels.py:359-365, gpt.py:51) do not exist;
 * ``GPU_TO_FLOPS`` has a ``"b200"`` entry, and ``executed_fwd_flops`` counts what the tensor
@@ -18,6 +23,7 @@ Forward/eval only: in the reference the training branch cannot run either (gpt.p
 config field that gpt.py:129 does not define).
 """
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -49,26 +55,55 @@ def _ln_flops(tokens, h):
 
 
 class _OperandCache:
-    """PackedWeight per parameter; rebuilt when the parameter is replaced, cast, moved or
-    written in place (torch bumps ``_version`` on in-place writes)."""
+    """Derived operands (PackedWeight and friends) per parameter; rebuilt when the parameter is replaced, cast,
+    moved or written in place.  The tag uses the Parameter's own ``_version``, which ``load_state_dict``,
+    ``param.copy_`` and optimizer steps bump (``param.data`` is a fresh tensor object whose counter always reads 0,
+    so it cannot serve).  Writes made *through* ``param.data`` (``param.data.mul_(2)``) bump no counter torch
+    exposes: after such a write call ``refresh_operands()`` on the model."""
 
     def __init__(self):
         self._slots = {}
 
-    def __call__(self, param, weight_is_nk=False):
-        t = param.data
-        tag = (t.data_ptr(), t._version, t.dtype, t.device, tuple(t.shape))
-        slot = self._slots.get(id(param))
+    def clear(self):
+        self._slots.clear()
+
+    @staticmethod
+    def _tag(param):
+        return (param.data_ptr(), param._version, param.dtype, param.device, tuple(param.shape))
+
+    def derived(self, key, params, make):
+        """`make()` cached under `key` until one of `params` changes."""
+        tag = tuple(self._tag(p) for p in params)
+        slot = self._slots.get(key)
         if slot is None or slot[0] != tag:
-            slot = (tag, K.pack_weight(t.contiguous(), weight_is_nk=weight_is_nk))
-            self._slots[id(param)] = slot
+            slot = (tag, make())
+            self._slots[key] = slot
         return slot[1]
+
+    def __call__(self, param, weight_is_nk=False):
+        return self.derived(("packed", id(param), weight_is_nk), (param,),
+                            lambda: K.pack_weight(param.data.contiguous(), weight_is_nk=weight_is_nk))
+
+    def folded(self, weight, ln_weight, ln_bias, bias):
+        """FoldedWeight of `weight` with the LayerNorm (ln_weight, ln_bias) in front of it and `bias` behind."""
+        return self.derived(("folded", id(weight)), (weight, ln_weight, ln_bias, bias),
+                            lambda: K.fold_layer_norm(weight.data.contiguous(), ln_weight.data.contiguous(), ln_bias.data.contiguous(),
+                                                      bias.data.contiguous()))
 
 
 class _EvalOnly(nn.Module):
     def _check_eval(self):
         if self.training:
             raise NotImplementedError("libb200gpt implements the forward/eval path only: call .eval() first")
+
+    def refresh_operands(self):
+        """Drop every cached derived operand (packed weights) of this module and its children; the next forward
+        rebuilds them from the parameters.  Needed only after writes through ``param.data``, which torch's version
+        counters do not see; ``load_state_dict``, ``copy_``, casts and moves are noticed without it."""
+        for m in self.modules():
+            cache = getattr(m, "_operand", None)
+            if isinstance(cache, _OperandCache):
+                cache.clear()
 
 
 class FusedAttention(_EvalOnly):
@@ -89,6 +124,17 @@ class FusedAttention(_EvalOnly):
         q, k, v = K.matmul_and_split_qkv(y, self._operand(self.c_attn_weight), self.c_attn_bias.data, self.num_heads)
         y = K.flash_attention_v1(q, k, v, merged_heads=True).view(skip.shape)
         return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=skip)
+
+    def forward_folded(self, x, stats, return_row_stats=True):
+        """The same block with its LayerNorm folded into c_attn: x (batch, seqlen, hidden) are the raw rows,
+        `stats` their RowStats.  Returns (output, RowStats of the output) for the block that follows."""
+        self._check_eval()
+        w = self._operand.folded(self.c_attn_weight, self.layer_norm_weight, self.layer_norm_bias, self.c_attn_bias)
+        q, k, v = K.split_qkv(K.fused_ffn(x, w, ln_stats=stats), self.num_heads)
+        y = K.flash_attention_v1(q, k, v, merged_heads=True).view(x.shape)
+        if not return_row_stats:
+            return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=x), None
+        return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=x, return_row_stats=True)
 
     def get_fwd_flops(self, num_tokens):
         h = self.hidden_size
@@ -112,6 +158,15 @@ class FusedMLP(_EvalOnly):
         y = K.fused_ffn(y, self._operand(self.ffn1_weight), bias=self.ffn1_bias.data, add_gelu=True)
         return K.fused_ffn(y, self._operand(self.ffn2_weight), bias=self.ffn2_bias.data, residual=x)
 
+    def forward_folded(self, x, stats, return_row_stats=True):
+        """The same block with its LayerNorm folded into ffn1 (see FusedAttention.forward_folded)."""
+        self._check_eval()
+        w = self._operand.folded(self.ffn1_weight, self.layer_norm_weight, self.layer_norm_bias, self.ffn1_bias)
+        y = K.fused_ffn(x, w, add_gelu=True, ln_stats=stats)
+        if not return_row_stats:
+            return K.fused_ffn(y, self._operand(self.ffn2_weight), bias=self.ffn2_bias.data, residual=x), None
+        return K.fused_ffn(y, self._operand(self.ffn2_weight), bias=self.ffn2_bias.data, residual=x, return_row_stats=True)
+
     def get_fwd_flops(self, num_tokens):
         h, mid = self.hidden_size, self.intermediate_size
         return _ln_flops(num_tokens, h) + _linear_flops(num_tokens, h, mid) + _linear_flops(num_tokens, mid, h)
@@ -128,6 +183,11 @@ class GPTConfig:
 
 
 class FusedGPT(_EvalOnly):
+    # Fold the LayerNorms of the blocks into the GEMMs behind them (16-bit models; see the module docstring).  The
+    # environment variable B200GPT_FOLD_LAYERNORM=0 changes the default for the process; the attribute can also be set
+    # per model.
+    fold_layer_norm = os.environ.get("B200GPT_FOLD_LAYERNORM", "1") != "0"
+
     def __init__(self, config):
         super().__init__()
         self.config = config
@@ -145,9 +205,16 @@ class FusedGPT(_EvalOnly):
     def forward(self, x):
         """ids (batch, seqlen) -> final hidden state (batch, seqlen, n_embd)."""
         self._check_eval()
-        y = K.fused_embeddings(x, self.wte_weight.data, self.wpe_weight.data)
-        for attention, mlp in self.blocks:
-            y = mlp(attention(y))
+        if self.fold_layer_norm and self.wte_weight.dtype in (torch.float16, torch.bfloat16) and self.config.n_embd % 8 == 0:
+            y, stats = K.fused_embeddings(x, self.wte_weight.data, self.wpe_weight.data, return_row_stats=True)
+            last = len(self.blocks) - 1
+            for i, (attention, mlp) in enumerate(self.blocks):
+                y, stats = attention.forward_folded(y, stats)
+                y, stats = mlp.forward_folded(y, stats, return_row_stats=i != last)  # the final LayerNorm stays a kernel
+        else:
+            y = K.fused_embeddings(x, self.wte_weight.data, self.wpe_weight.data)
+            for attention, mlp in self.blocks:
+                y = mlp(attention(y))
         return K.fused_layer_norm(y, self.layer_norm_weight.data, self.layer_norm_bias.data)
 
     @torch.no_grad()
@@ -230,21 +297,33 @@ class GraphedForward:
 
     def __init__(self, model, example_ids, what="logits", warmup=3):
         assert what in ("forward", "logits", "logits_and_next_ids", "next_ids")
+        self._model, self._warmup = model, warmup
         self._fn = getattr(model, what)
         self.static_ids = example_ids.clone()
+        self._capture()
+
+    def _signature(self):
+        return tuple(_OperandCache._tag(p) for p in self._model.parameters())
+
+    def _capture(self):
+        dev = self.static_ids.device
         # warm-up on a side stream: first calls set kernel attributes, pack weights and fill the allocator's pool
-        side = torch.cuda.Stream(device=example_ids.device)
-        side.wait_stream(torch.cuda.current_stream(example_ids.device))
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side), torch.no_grad():
-            for _ in range(max(1, warmup)):
+            for _ in range(max(1, self._warmup)):
                 self._fn(self.static_ids)
-        torch.cuda.current_stream(example_ids.device).wait_stream(side)
+        torch.cuda.current_stream(dev).wait_stream(side)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph), torch.no_grad():
             self.outputs = self._fn(self.static_ids)
+        self._sig = self._signature()
 
     def __call__(self, ids):
         assert ids.shape == self.static_ids.shape, "a captured forward serves one (batch, seqlen) only"
+        if self._signature() != self._sig:
+            # a parameter was reloaded, cast or replaced since the capture: the graph holds the old packed operands
+            self._capture()
         self.static_ids.copy_(ids)
         self.graph.replay()
         return self.outputs

@@ -11,7 +11,11 @@ Differences, all deliberate:
 * ``matmul_and_split_qkv`` returns q, k, v as strided views into one fused buffer instead of
   three transposed copies (kernels.py:359-365), and ``flash_attention_v1`` accepts such views;
 * keyword-only extras (``weight_is_nk``, ``merged_heads``, ``out`` ...) used by the model to
-  avoid copies; defaults reproduce the reference's behaviour.
+  avoid copies; defaults reproduce the reference's behaviour;
+* LayerNorm folded into the following GEMM (the fusion the reference leaves as a TODO, kernels.py:132-133):
+  ``fold_layer_norm`` prepares the weights once, ``fused_ffn(..., ln_stats=...)`` consumes the raw rows with
+  their ``RowStats`` (mean, rstd per row), which ``fused_embeddings`` / ``fused_ffn(..., return_row_stats=True)`` /
+  ``row_stats`` produce -- the normalised activations are never written (16-bit dtypes only).
 
 Every operator launches on torch's current CUDA stream and never synchronises.  There is
 no CPU path: tensors must live on a CUDA device and the shared library must be built.
@@ -28,6 +32,7 @@ from ._lib import check, dtype_code, require_cuda, stream_ptr
 _lib.load()  # fail at import time, loudly, if the extension is not built
 
 LN_EPS = 1e-5  # kernels.py:106
+LN_EXT_COLS = 64  # B200_LN_EXT_COLS: width of the row / weight extensions of a folded LayerNorm
 
 
 def _no_dropout(p):
@@ -88,9 +93,49 @@ def _same_device(*tensors):
 
 
 # ----------------------------------------------------------------------------- embeddings
+class RowStats:
+    """LayerNorm statistics of the rows of an (M, cols) matrix: ``data[row] = (mean, 1 / sqrt(variance + eps))``,
+    float32, shape (M, 2), variance biased -- the two numbers the reference's fused_layer_norm derives per row
+    (kernels.py:116-130).  Producers: ``fused_embeddings(..., return_row_stats=True)``, ``row_stats`` and
+    ``fused_ffn(..., return_row_stats=True)``; consumer: ``fused_ffn(..., ln_stats=...)``.  For 16-bit rows ``ext``
+    (M, 64) holds, in the rows' dtype, the "row extension" the consuming GEMM multiplies as one extra k-block
+    (-mean and 1/rstd as high/low parts; see include/b200_gpt.h); None for float32 rows."""
+
+    __slots__ = ("data", "cols", "ext")
+
+    def __init__(self, data, cols, ext=None):
+        self.data, self.cols, self.ext = data, cols, ext
+
+    @property
+    def mean(self):
+        return self.data[:, 0]
+
+    @property
+    def rstd(self):
+        return self.data[:, 1]
+
+
 @torch.no_grad()
-def fused_embeddings(x, wte, wpe, dropout_prob=0.0):
-    """z[b, l, :] = wte[x[b, l], :] + wpe[l, :]  (reference kernels.py:76-101)."""
+def row_stats(x):
+    """RowStats of the rows of x (*, H) (the statistics half of the reference's fused_layer_norm,
+    kernels.py:116-130): what ``fused_ffn(..., ln_stats=...)`` needs for rows that no operator of this
+    library produced."""
+    require_cuda(x)
+    assert x.is_contiguous()
+    H = x.shape[-1]
+    M = x.numel() // H if H else 0
+    data = torch.empty((max(M, 1), 2), device=x.device, dtype=torch.float32)
+    ext = torch.empty((max(M, 1), LN_EXT_COLS), device=x.device, dtype=x.dtype) if x.dtype != torch.float32 else None
+    with torch.cuda.device(x.device):
+        st = _lib.load().b200_row_ln_stats(x.data_ptr(), data.data_ptr(), _ptr(ext), M, H, LN_EPS, dtype_code(x.dtype), stream_ptr(x.device))
+    check(st, "row_stats")
+    return RowStats(data[:M], H, None if ext is None else ext[:M])
+
+
+@torch.no_grad()
+def fused_embeddings(x, wte, wpe, dropout_prob=0.0, *, return_row_stats=False):
+    """z[b, l, :] = wte[x[b, l], :] + wpe[l, :]  (reference kernels.py:76-101).  With ``return_row_stats`` the
+    result is ``(z, RowStats of z's rows)``, taken while the rows are written."""
     _no_dropout(dropout_prob)
     require_cuda(x, wte, wpe)
     assert wte.shape[1] == wpe.shape[1]
@@ -106,6 +151,14 @@ def fused_embeddings(x, wte, wpe, dropout_prob=0.0):
     if x.dtype != torch.int64:
         x = x.to(torch.int64)
     z = torch.empty((B * L, H), device=dev, dtype=wte.dtype)
+    if return_row_stats:
+        stats = torch.empty((max(B * L, 1), 2), device=dev, dtype=torch.float32)
+        ext = torch.empty((max(B * L, 1), LN_EXT_COLS), device=dev, dtype=wte.dtype) if wte.dtype != torch.float32 else None
+        with torch.cuda.device(dev):
+            st = _lib.load().b200_embedding_ln_stats(x.data_ptr(), wte.data_ptr(), wpe.data_ptr(), z.data_ptr(), B, L, V, P, H,
+                                                     dtype_code(wte.dtype), None, LN_EPS, stats.data_ptr(), _ptr(ext), stream_ptr(dev))
+        check(st, "fused_embeddings")
+        return z.view((B, L, H)), RowStats(stats[:B * L], H, None if ext is None else ext[:B * L])
     with torch.cuda.device(dev):
         st = _lib.load().b200_embedding(x.data_ptr(), wte.data_ptr(), wpe.data_ptr(), z.data_ptr(), B, L, V, P, H,
                                         dtype_code(wte.dtype), None, stream_ptr(dev))
@@ -173,9 +226,96 @@ def pack_weight(weight, *, weight_is_nk=False):
     return PackedWeight(packed, K, N, weight.dtype)
 
 
+class FoldedWeight:
+    """A (K, N) GEMM weight with the LayerNorm that precedes it folded in (``fold_layer_norm``): ``data`` (N, K)
+    K-major 16-bit = LayerNorm weight * weight; ``colsum`` (N,) float32 its column sums and ``bias`` (N,) float32 =
+    bias + LayerNorm bias @ weight; ``ext`` (N, 64) the "weight extension" made of the two, which the consuming
+    GEMM multiplies as one extra k-block."""
+
+    __slots__ = ("data", "colsum", "bias", "ext", "K", "N", "storage_dtype")
+
+    def __init__(self, data, colsum, bias, ext, K, N, storage_dtype):
+        self.data, self.colsum, self.bias, self.ext, self.K, self.N, self.storage_dtype = data, colsum, bias, ext, K, N, storage_dtype
+
+
+@torch.no_grad()
+def fold_layer_norm(weight, ln_weight, ln_bias, bias=None):
+    """Fold ``fused_layer_norm(x, ln_weight, ln_bias)`` into the GEMM ``fused_ffn(., weight, bias)`` that follows it
+    (reference gpt.py:40-43, 94-101; its author's TODO at kernels.py:132-133):
+
+        LN(x) @ W + b = rstd * (x @ (g * W) - mean * colsum(g * W) + (beta @ W + b) / rstd)
+
+    Returns the FoldedWeight that ``fused_ffn(x, folded, ln_stats=RowStats of x)`` takes.  16-bit dtypes with
+    K % 8 == 0 only; done once per weight version, not per forward."""
+    require_cuda(weight, ln_weight, ln_bias, bias)
+    assert weight.dim() == 2 and weight.is_contiguous() and weight.dtype in (torch.float16, torch.bfloat16)
+    K, N = weight.shape
+    assert K % 8 == 0, "the folded operand is used in place: K must be a multiple of 8"
+    assert ln_weight.shape == (K,) and ln_bias.shape == (K,) and ln_weight.dtype == ln_bias.dtype == weight.dtype
+    assert ln_weight.is_contiguous() and ln_bias.is_contiguous()
+    if bias is not None:
+        assert bias.shape == (N,) and bias.dtype == weight.dtype and bias.is_contiguous()
+    dev = _same_device(weight, ln_weight, ln_bias, bias)
+    data = torch.empty((N, K), device=dev, dtype=weight.dtype)
+    colsum = torch.empty((N,), device=dev, dtype=torch.float32)
+    fbias = torch.empty((N,), device=dev, dtype=torch.float32)
+    ext = torch.empty((N, LN_EXT_COLS), device=dev, dtype=weight.dtype)
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_fold_layernorm(weight.data_ptr(), ln_weight.data_ptr(), ln_bias.data_ptr(), _ptr(bias), data.data_ptr(),
+                                             colsum.data_ptr(), fbias.data_ptr(), ext.data_ptr(), K, N, K, dtype_code(weight.dtype),
+                                             stream_ptr(dev))
+    check(st, "fold_layer_norm")
+    return FoldedWeight(data, colsum, fbias, ext, K, N, weight.dtype)
+
+
+def _ffn_layer_norm_aware(x, weight, bias, residual, add_gelu, out, ln_stats, return_row_stats):
+    """fused_ffn through b200_gemm_ln: either consuming RowStats (weight a FoldedWeight) or producing them."""
+    lead = x.shape[:-1]
+    x = x.view((-1, x.shape[-1]))
+    M, K = x.shape
+    assert isinstance(weight, (FoldedWeight, PackedWeight))
+    N = weight.N
+    assert K == weight.K and weight.storage_dtype == x.dtype and x.dtype in (torch.float16, torch.bfloat16)
+    assert x.is_contiguous() and K % 8 == 0 and x.data_ptr() % 16 == 0
+    assert (ln_stats is not None) != bool(return_row_stats), "one launch either consumes or produces row statistics"
+    dev = _same_device(x, weight.data, bias, residual)
+    z = torch.empty((M, N), device=dev, dtype=x.dtype) if out is None else out
+    assert z.shape == (M, N) and z.dtype == x.dtype and z.stride(1) == 1 and z.device == dev
+    if residual is not None:
+        residual = residual.view((M, N))
+        assert residual.is_contiguous() and residual.dtype == x.dtype
+    ld_out = z.stride(0) if M > 1 else max(N, z.stride(0))
+    lib = _lib.load()
+    dt = dtype_code(x.dtype)
+    stats_out = None
+    with torch.cuda.device(dev):
+        if ln_stats is not None:
+            assert isinstance(weight, FoldedWeight), "ln_stats needs the FoldedWeight made by fold_layer_norm"
+            assert bias is None, "the bias is part of the FoldedWeight"
+            assert ln_stats.cols == K and ln_stats.data.shape[0] >= M and ln_stats.data.device == dev and ln_stats.data.is_contiguous()
+            assert ln_stats.ext is not None and ln_stats.ext.dtype == x.dtype and ln_stats.ext.is_contiguous() and ln_stats.ext.shape[0] >= M
+            st = lib.b200_gemm_ln(x.data_ptr(), weight.data.data_ptr(), None, _ptr(residual), z.data_ptr(), M, N, K, K, weight.data.stride(0),
+                                  N, ld_out, dt, dt, int(bool(add_gelu)), ln_stats.data.data_ptr(), ln_stats.ext.data_ptr(),
+                                  weight.ext.data_ptr(), None, None, LN_EPS, None, 0, _status_ptr(dev), stream_ptr(dev))
+        else:
+            assert isinstance(weight, PackedWeight) and not add_gelu
+            if bias is not None:
+                assert bias.is_contiguous() and bias.shape[0] == N and bias.dtype == x.dtype
+            stats_out = torch.empty((max(M, 1), 2), device=dev, dtype=torch.float32)
+            ext_out = torch.empty((max(M, 1), LN_EXT_COLS), device=dev, dtype=x.dtype)
+            need = lib.b200_gemm_ln_workspace_bytes(M, N)
+            ws = torch.empty((max(need, 16),), device=dev, dtype=torch.uint8)
+            st = lib.b200_gemm_ln(x.data_ptr(), weight.data.data_ptr(), _ptr(bias), _ptr(residual), z.data_ptr(), M, N, K, K,
+                                  weight.data.stride(0), N, ld_out, dtype_code(weight.data.dtype), dt, 0, None, None, None,
+                                  stats_out.data_ptr(), ext_out.data_ptr(), LN_EPS, ws.data_ptr(), need, _status_ptr(dev), stream_ptr(dev))
+    check(st, "fused_ffn(layer norm)")
+    zz = z if out is not None else z.view((*lead, N))
+    return (zz, RowStats(stats_out[:M], N, ext_out[:M])) if return_row_stats else zz
+
+
 @torch.no_grad()
 def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=0.0, *, weight_is_nk=False, out=None,
-              return_argmax=False, return_lse=False):
+              return_argmax=False, return_lse=False, ln_stats=None, return_row_stats=False):
     """z = [gelu_new](x @ weight + bias) + residual  (reference kernels.py:261-315).
 
     x (*, K); weight (K, N) -- or (N, K) with ``weight_is_nk=True``, or a PackedWeight;
@@ -185,8 +325,17 @@ def fused_ffn(x, weight, bias=None, residual=None, add_gelu=False, dropout_prob=
     is ``(z, ids)``, ids (M,) int64 being the argmax over each row of z (lowest column on ties),
     produced by the GEMM's epilogue rather than by a second pass over z; with ``return_lse=True`` as well,
     ``(z, ids, lse)`` where lse (M,) float32 is log(sum_j exp(z[row, j])).
+
+    LayerNorm fusion (16-bit dtypes, N % 8 == 0): with ``ln_stats`` (the RowStats of x's rows) and ``weight`` a
+    FoldedWeight, x is the RAW input of a LayerNorm and z = [gelu](LN(x) @ W + b) + residual without the
+    normalised tensor; with ``return_row_stats=True`` (``weight`` a PackedWeight, no GELU) the result is
+    ``(z, RowStats of z's rows)`` for the next folded GEMM.
     """
     _no_dropout(dropout_prob)
+    if ln_stats is not None or return_row_stats:
+        assert not (return_argmax or return_lse)
+        require_cuda(x, bias, residual)
+        return _ffn_layer_norm_aware(x, weight, bias, residual, add_gelu, out, ln_stats, return_row_stats)
     packed = weight if isinstance(weight, PackedWeight) else None
     require_cuda(x, None if packed else weight, bias, residual)
     out_shape_0 = x.shape[:-1]
@@ -310,7 +459,12 @@ def matmul_and_split_qkv(x, weight, bias, num_heads):
     Returns q, k, v of logical shape (batch, heads, seqlen, head_size) -- as views into the
     single (batch, seqlen, 3*hidden) projection output rather than transposed copies.
     """
-    x = fused_ffn(x, weight, bias=bias)
+    return split_qkv(fused_ffn(x, weight, bias=bias), num_heads)
+
+
+def split_qkv(x, num_heads):
+    """(batch, seqlen, 3 * hidden) projection output -> q, k, v views of logical shape (batch, heads, seqlen,
+    head_size): the head split of the reference (kernels.py:355-365) without its three transposed copies."""
     batch_size, seqlen, hidden_size = x.shape
     assert hidden_size % 3 == 0, hidden_size
     hidden_size = hidden_size // 3

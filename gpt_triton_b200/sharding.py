@@ -46,22 +46,46 @@ def gather_rows(local, n_rows_total, group=None):
     return torch.cat([p[:n] for p, n in zip(parts, sizes)], dim=0)
 
 
+def gather_equal_rows(local, out=None, group=None):
+    """All-gather row blocks of EQUAL size with one ``all_gather_into_tensor`` straight into `out`
+    ((world * rows, ...), allocated if None): no padding, no list of parts, no concatenation.  The per-step
+    collective of a batch that divides evenly over the ranks."""
+    world = dist.get_world_size(group)
+    local = local.contiguous()
+    if out is None:
+        out = torch.empty((world * local.shape[0], *local.shape[1:]), dtype=local.dtype, device=local.device)
+    elif out.shape[0] != world * local.shape[0] or out.shape[1:] != local.shape[1:] or not out.is_contiguous():
+        raise ValueError(f"out has shape {tuple(out.shape)}, expected ({world * local.shape[0]}, ...) contiguous")
+    dist.all_gather_into_tensor(out, local, group=group)
+    return out
+
+
 @torch.no_grad()
-def sharded_forward(logits_fn, ids, gather="argmax", group=None):
-    """Run `logits_fn` (ids -> logits) on this rank's rows of the global batch `ids` and return
-    the gathered result on every rank:
+def sharded_forward(fn, ids, gather="argmax", group=None, fn_returns="logits"):
+    """Run `fn` on this rank's rows of the global batch `ids` and return the gathered result on every rank.
+
+    `fn` maps ids to logits (``fn_returns="logits"``, e.g. ``FusedGPT.logits``) or straight to next-token ids
+    (``fn_returns="ids"``, e.g. ``FusedGPT.next_ids``, whose argmax comes out of the lm_head's epilogue so that
+    no (tokens, vocab) tensor is written or reduced a second time).
 
     gather="argmax": (batch, seqlen) int64 next-token ids (8 bytes per token cross NVLink);
     gather="logits": (batch, seqlen, vocab) logits (large: meant for checks, not for throughput);
-    gather="none":   this rank's logits only, no collective.
+    gather="none":   this rank's result only, no collective.
     """
+    if fn_returns not in ("logits", "ids"):
+        raise ValueError(f"unknown fn_returns {fn_returns!r}")
+    if gather not in ("none", "argmax", "logits"):
+        raise ValueError(f"unknown gather mode {gather!r}")
+    if fn_returns == "ids" and gather == "logits":
+        raise ValueError("a callable that returns ids has no logits to gather")
     world = dist.get_world_size(group)
     local_ids = shard_batch(ids, dist.get_rank(group), world)
-    logits = logits_fn(local_ids)
+    result = fn(local_ids)
     if gather == "none":
-        return logits
+        return result
     if gather == "argmax":
-        return gather_rows(logits.argmax(dim=-1), ids.shape[0], group)
-    if gather == "logits":
-        return gather_rows(logits.contiguous(), ids.shape[0], group)
-    raise ValueError(f"unknown gather mode {gather!r}")
+        local = result if fn_returns == "ids" else result.argmax(dim=-1)
+        if ids.shape[0] % world == 0:
+            return gather_equal_rows(local, group=group)
+        return gather_rows(local, ids.shape[0], group)
+    return gather_rows(result.contiguous(), ids.shape[0], group)

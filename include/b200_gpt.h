@@ -35,7 +35,7 @@ enum {
 const char* b200_status_string(int status);
 /* cudaGetErrorString of the last failing CUDA call made by this library on this thread. */
 const char* b200_last_cuda_error(void);
-/* ABI version of this header (4); bumped when a signature changes or an entry point is added. */
+/* ABI version of this header (5); bumped when a signature changes or an entry point is added. */
 int b200_abi_version(void);
 /* Number of kernels this library has launched in this process so far (all entry points). */
 uint64_t b200_launch_count(void);
@@ -53,12 +53,79 @@ int b200_embedding(const int64_t* ids, const void* wte, const void* wpe, void* o
 /*
  * Row LayerNorm with fp32 statistics: out = (x - mean) * rsqrt(var + eps) * w + b.
  * Stands in for fused_layer_norm (kernels.py:149-164; kernel kernels.py:104-145).
- * x [M,H], w [H], b [H] of in_dtype; out [M,H] of out_dtype (the reference always has
- * out_dtype == in_dtype; a 16-bit out_dtype from fp32 input gives the same bits the
- * following GEMM would have produced by rounding its operand).
+ * x [M,H], w [H], b [H] of in_dtype; out [M,H] of out_dtype.  The reference always has
+ * out_dtype == in_dtype; the (in, out) pairs built here are F32->F32, F16->F16, BF16->BF16
+ * and F32->F16 / F32->BF16 (a 16-bit output from fp32 input gives the bits the following
+ * GEMM would have produced by rounding its operand).  Any other pair of valid dtype codes
+ * returns B200_ERR_UNSUPPORTED.
  */
 int b200_layernorm(const void* x, const void* w, const void* b, void* out, int64_t M, int64_t H, float eps,
                    int in_dtype, int out_dtype, void* stream);
+
+/*
+ * LayerNorm folded into the GEMM that follows it (the fusion the reference's author leaves as a TODO at
+ * kernels.py:132-133): for a row x with statistics (mean, rstd), LayerNorm weight g and bias beta,
+ *   LN(x) . w + bias = rstd * ( x . (g*w)  -  mean * colsum(g*w)  +  (1/rstd) * (beta . w + bias) ),
+ * so a GEMM can take the RAW rows x and the normalised activations never exist in memory.  The two rank-one
+ * terms are added by the tensor cores themselves: every row carries a 64-element "row extension"
+ * [-mean, 1/rstd as high/low 16-bit parts, 0 ...] and every output column a "weight extension"
+ * [colsum, beta.w + bias as high/low parts, 0 ...]; the consuming GEMM runs one extra 64-wide k-block over the
+ * two, and its epilogue only multiplies by rstd.  B200_LN_EXT_COLS is the width of both extensions; they are of
+ * the model's 16-bit dtype.  The entry points below produce and consume these pieces.
+ */
+#define B200_LN_EXT_COLS 64
+
+/*
+ * b200_embedding that also returns the LayerNorm statistics of every row it stores:
+ * ln_stats_out (fp32 pairs, [B*L][2], 8-byte aligned) receives (mean, 1 / sqrt(variance + eps)) over the H
+ * stored (rounded) values of the row, variance biased, both in fp32: exactly the two numbers
+ * fused_layer_norm derives per row (kernels.py:116-130 of the reference).  ln_ext_out (optional; 16-bit dtype
+ * only; [B*L][B200_LN_EXT_COLS] of `dtype`, 16-byte aligned) receives the rows' extensions.
+ */
+int b200_embedding_ln_stats(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t B, int64_t L, int64_t V,
+                            int64_t P, int64_t H, int dtype, int* bad_id_flag, float eps, float* ln_stats_out, void* ln_ext_out, void* stream);
+
+/*
+ * LayerNorm statistics (and optionally row extensions) of the rows of an existing x [M,H] of `dtype`:
+ * the statistics half of fused_layer_norm (kernels.py:116-130) without the normalised output.  Entry into a
+ * chain of b200_gemm_ln calls for rows that no kernel of this library made.
+ */
+int b200_row_ln_stats(const void* x, float* ln_stats_out, void* ln_ext_out, int64_t M, int64_t H, float eps, int dtype, void* stream);
+
+/*
+ * Weight-side half of the fold, done once per weight version.  From w [K,N] row-major (the state-dict layout
+ * of c_attn / c_fc), gamma and beta [K] (LayerNorm weight and bias) and bias [N] or NULL, all of the 16-bit
+ * `dtype`, this writes
+ *   packed [N, ld_packed] K-major (ld_packed >= K, a multiple of 8; tail columns zero) = round(gamma[k]*w[k,n]),
+ *   colsum [N] fp32 = sum over k of the rounded packed values,   bias_out [N] fp32 = bias + beta . w,
+ *   w_ext [N, B200_LN_EXT_COLS] of `dtype` (16-byte aligned) = the weight extensions made of those two.
+ * B200_ERR_UNSUPPORTED for B200_F32 (the fp32 path keeps LayerNorm apart).
+ */
+int b200_fold_layernorm(const void* w, const void* gamma, const void* beta, const void* bias, void* packed, float* colsum, float* bias_out,
+                        void* w_ext, int64_t K, int64_t N, int64_t ld_packed, int dtype, void* stream);
+
+/*
+ * b200_gemm with a LayerNorm on one side of it; io_dtype == op_dtype, 16-bit; 16-byte aligned out/residual
+ * with pitches that are multiples of 8 elements (else B200_ERR_UNSUPPORTED).  Exactly one role per call:
+ *
+ * Consumer (ln_stats != NULL, ln_stats_out == NULL): A holds the RAW rows x [M,K], ln_stats[row] their
+ * (mean, rstd), ln_ext [M, B200_LN_EXT_COLS] their extensions, B the `packed` weights and w_ext the weight
+ * extensions of b200_fold_layernorm; stores [gelu](LN(x) . w + bias) + residual.  `bias` must be NULL (it is
+ * inside w_ext).  Replaces fused_layer_norm + fused_ffn (gpt.py:40-43, 94-101) without the normalised
+ * tensor; differs from that pair by roundings only (the normalised row is not rounded to 16 bits before the
+ * product).
+ *
+ * Producer (ln_stats_out != NULL, ln_stats == NULL, add_gelu == 0): plain b200_gemm that also leaves
+ * ln_stats_out[row] = (mean, 1 / sqrt(variance + eps)) over the N columns of every row it stores (taken from
+ * the fp32 values before they are rounded) and ln_ext_out [M, B200_LN_EXT_COLS], ready for a following
+ * consumer call.  The epilogue writes per-128-column partial sums to `workspace`
+ * (b200_gemm_ln_workspace_bytes(M, N) bytes, 16-byte aligned) and a small second kernel merges them.
+ */
+size_t b200_gemm_ln_workspace_bytes(int64_t M, int64_t N);
+int b200_gemm_ln(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                 int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, int io_dtype, int add_gelu, const float* ln_stats,
+                 const void* ln_ext, const void* w_ext, float* ln_stats_out, void* ln_ext_out, float eps, void* workspace, size_t workspace_bytes,
+                 int* status_word, void* stream);
 
 /*
  * Operand packing for b200_gemm: dst[r, c] = cast(src[r, c]) (transpose == 0) or
@@ -140,10 +207,13 @@ int b200_ffn(const void* x, const void* w, const void* bias, const void* residua
  * workspace: the packed operands go to an array of B200_FFN_STATIC_SCRATCH_BYTES that is part of the
  * library image on every GPU that loads it (held until the process exits).  The call makes no
  * cudaMalloc/cudaFree or other allocating call.
- *  - Limit: if the operands, both packed (b200_ffn_workspace_bytes(M, N, K, 0, B200_F32) bytes),
- *    exceed B200_FFN_STATIC_SCRATCH_BYTES the call returns B200_ERR_WORKSPACE and launches nothing.
+ *  - Limit: what this call has to pack (an operand is packed unless it is 16-bit, 16-byte aligned, has
+ *    K % 8 == 0 and, for w, the [N, K] layout; 2 * rows * roundup8(K) bytes each, rounded up to 256) must
+ *    fit B200_FFN_STATIC_SCRATCH_BYTES, else the call returns B200_ERR_WORKSPACE and launches nothing.
+ *    A call that packs nothing (e.g. the tied lm_head in fp16) is never refused for size.
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
- *    that device current); make that first call outside any stream capture.
+ *    that device current) and keeps it; make that first call outside any stream capture.  The address
+ *    belongs to the device's primary context: do not call again on a device after cudaDeviceReset.
  *  - Every call on a device shares the one array, which keeps the previous call's contents (nothing
  *    needs clearing: each call overwrites what it reads).  Two calls that may overlap on the GPU
  *    (different streams) race on it; serialise them.

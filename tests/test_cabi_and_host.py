@@ -32,7 +32,7 @@ def test_library_builds_and_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/b200_gpt.h but not exported"
     assert sorted(_lib.SIGNATURES) == names, "ctypes signature table and header disagree"
     bound = _lib.load()
-    assert bound.b200_abi_version() == 4
+    assert bound.b200_abi_version() == 5
     assert bound.b200_status_string(0) == b"ok"
     assert bound.b200_status_string(6) == b"a kernel abandoned a bounded wait"
 
@@ -53,6 +53,22 @@ def test_argument_checks_need_no_gpu():
     assert lib.b200_attention(None, None, None, None, 1, 1, 4, 24, strides, strides, strides, strides, 1.0, 0, 0, None, None) == 1
     assert lib.b200_gemm(None, None, None, None, None, 4, 4, 0, 8, 8, 4, 4, 1, 1, 0, None, None) == 1  # K = 0
     assert lib.b200_ffn(None, None, None, None, None, 0, 4, 4, 4, 0, 0, 1, None, 0, None, None) == 0  # M = 0
+    assert lib.b200_layernorm(ctypes.c_void_p(256), ctypes.c_void_p(256), ctypes.c_void_p(256), ctypes.c_void_p(256), 4, 8, 1e-5, 1, 2, None) == 4  # fp16 -> bf16 is not built
+    # LayerNorm-aware GEMM: exactly one role per call, 16-bit data only; the fold is not offered for fp32 weights
+    p256 = ctypes.c_void_p(256)
+    shape = (8, 8, 8, 8, 8, 8, 8)
+    assert lib.b200_gemm_ln(p256, p256, None, None, p256, *shape, 1, 1, 0, None, None, None, None, None, 1e-5, None, 0, None, None) == 1
+    assert lib.b200_gemm_ln(p256, p256, None, None, p256, *shape, 1, 0, 0, None, None, None, p256, p256, 1e-5, p256, 1 << 20, None, None) == 4
+    assert lib.b200_gemm_ln(p256, p256, None, None, p256, *shape, 1, 1, 0, None, None, None, p256, p256, 1e-5, None, 0, None, None) == 5  # producer needs its workspace
+    assert lib.b200_gemm_ln(p256, p256, None, None, p256, *shape, 1, 1, 0, p256, None, p256, None, None, 1e-5, None, 0, None, None) == 1  # consumer needs the row extensions
+    assert lib.b200_gemm_ln(p256, p256, None, None, p256, *shape, 1, 2, 0, p256, p256, p256, None, None, 1e-5, None, 0, None, None) == 4  # operand and storage type must agree
+    assert lib.b200_gemm_ln_workspace_bytes(100, 768) == 6 * 128 * 8 and lib.b200_gemm_ln_workspace_bytes(100, 1600) == 13 * 128 * 8
+    assert lib.b200_fold_layernorm(p256, p256, p256, None, p256, p256, p256, p256, 8, 8, 8, 0, None) == 4
+    assert lib.b200_fold_layernorm(p256, p256, p256, None, p256, p256, p256, p256, 8, 8, 4, 1, None) == 1  # ld_packed < K
+    assert lib.b200_row_ln_stats(None, None, None, 0, 8, 1e-5, 1, None) == 0 and lib.b200_row_ln_stats(None, None, None, 4, 8, 1e-5, 1, None) == 1
+    # sizes beyond what the GEMM indexes are refused before any arithmetic on them
+    assert lib.b200_ffn(p256, p256, None, None, p256, 1 << 40, 8, 8, 8, 0, 0, 1, None, 0, None, None) == 1
+    assert lib.b200_ffn_static_scratch(p256, p256, None, None, p256, 1 << 40, 8, 1 << 40, 8, 0, 0, 0, None, None) == 1
     assert lib.b200_selftest_bounded_wait(None, 1000, None) == 1  # needs a status word
     assert lib.b200_selftest_bounded_wait(ctypes.c_void_p(256), 0, None) == 1  # and a positive cycle limit
     # row statistics without the product: argmax_out is mandatory, targets and target_logit_out come together,

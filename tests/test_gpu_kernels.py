@@ -393,6 +393,32 @@ def test_attention_sweep_shapes_fp16(S):
     assert torch.equal(z[:, :, :100], z2[:, :, :100])
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("layout", ["contiguous", "fused_qkv"])
+def test_attention_seq_2048_vs_oracle(dtype, layout):
+    """The longest kernel-sweep sequence, S = 2048 (B=2, H=12, D=64): 16 query tiles per (batch, head) and up to 32
+    key blocks per tile, i.e. the longest chain of online-softmax rescales and the deepest longest-first work
+    ordering the tensor-core kernel sees; every output row against the oracle."""
+    g = torch.Generator().manual_seed(2048)
+    B, N, S = 2, 12, 2048
+    if layout == "contiguous":
+        q, k, v = ((torch.randn((B, N, S, 64), generator=g) / 8).to(dtype) for _ in range(3))
+        qc, kc, vc = cu(q), cu(k), cu(v)
+    else:
+        qkv = (torch.randn((B, S, 3 * N * 64), generator=g) / 8).to(dtype)
+        q, k, v = (t.reshape(B, S, N, 64).transpose(1, 2) for t in qkv.split(N * 64, dim=2))
+        qc, kc, vc = (t.reshape(B, S, N, 64).transpose(1, 2) for t in cu(qkv).split(N * 64, dim=2))
+    ref = orc.flash_attention_v1(q.contiguous(), k.contiguous(), v.contiguous())
+    z = K().flash_attention_v1(qc, kc, vc)
+    assert_close(z, ref, scale_big=False, floor=ATTN_TOL)
+    merged = K().flash_attention_v1(qc, kc, vc, merged_heads=True)
+    assert torch.equal(merged.view(B, S, N, 64).transpose(1, 2), z)
+    # N(0,1) scores (16 times the variance): peaked rows, frequent changes of the running maximum
+    q2 = (q.float() * 8).to(dtype).contiguous()
+    ref2 = orc.flash_attention_v1(q2, k.contiguous(), v.contiguous())
+    assert_close(K().flash_attention_v1(cu(q2), kc, vc), ref2, scale_big=False, floor=ATTN_TOL)
+
+
 def test_attention_asserts():
     k = K()
     q = torch.rand(1, 2, 8, 24, device=DEV)

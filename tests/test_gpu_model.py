@@ -5,7 +5,7 @@ GPT-2-small shapes, and through batch-independence at the benchmark's full size.
 import pytest
 import torch
 
-from conftest import TINY, load_golden
+from conftest import TINY, load_golden, ulp_tolerance
 from oracle import gpt2_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -143,6 +143,97 @@ def test_bf16_medium_and_xl_shapes_vs_oracle(name, kw, B, L):
     assert (logits.cpu().float() - ref_logits.float()).abs().mean().item() < 0.015
     _argmax_agrees_where_clear(logits.cpu(), ref_logits, 6.25e-2)
     assert torch.equal(logits.gather(2, next_ids[..., None])[..., 0], logits.max(dim=-1).values)
+
+
+def _ulp_report(got, ref, dtype):
+    """(max-abs, largest and mean distance in units in the last place of `dtype` at the reference's magnitude)."""
+    d = (got.float() - ref.float()).abs()
+    u = d / ulp_tolerance(ref, dtype, 1.0)
+    return d.max().item(), u.max().item(), u.mean().item()
+
+
+@pytest.mark.parametrize("fold", [True, False])
+def test_bf16_medium_teacher_forced_per_block_in_ulps(fold):
+    """GPT-2 medium width (h=1024, 16 heads), bf16: every block fed the ORACLE's block input, so nothing
+    accumulates; compared in units in the last place of bf16 next to max-abs (one bf16 ulp is 1.6e-2 at
+    magnitude 2-4: max-abs alone says little).  The operator-by-operator path stays within 2 ulp of the oracle
+    in every block (absolute floor 4e-3 for values next to zero).  The LayerNorm-folded path omits one rounding of
+    the reference: about every fifth element of the 4h-wide ffn1 output then rounds the other way (one bf16 ulp,
+    4e-3 at magnitude 0.5-1), and ffn2 sums ~800 such flips times N(0, 0.02) weights: up to ~1.2e-2 on a block
+    output, the floor used for it here.  Exact arithmetic lies as close to the folded result as to the oracle's."""
+    from gpt_triton_b200 import kernels as K
+
+    kw = dict(vocab_size=50257, block_size=1024, n_layer=6, n_head=16, n_embd=1024, dropout=0.1)
+    model, cfg, sd = build_model(kw, torch.bfloat16)
+    ids = torch.randint(0, 50257, (2, 160), generator=torch.Generator().manual_seed(0))
+    x = orc.fused_embeddings(ids, sd["wte_weight"], sd["wpe_weight"])
+    assert torch.equal(K.fused_embeddings(ids.to(DEV), model.wte_weight.data, model.wpe_weight.data).cpu(), x)
+    limit = 3.0 if fold else 2.0
+    worst = 0.0
+    for i in range(cfg.n_layer):
+        ref_a = orc.attention_block(sd, f"blocks.{i}.0.", x, cfg.n_head)
+        xd = x.to(DEV)
+        got_a = model.blocks[i][0].forward_folded(xd, K.row_stats(xd))[0] if fold else model.blocks[i][0](xd)
+        ref_m = orc.mlp_block(sd, f"blocks.{i}.1.", ref_a)
+        rd = ref_a.to(DEV)
+        got_m = model.blocks[i][1].forward_folded(rd, K.row_stats(rd))[0] if fold else model.blocks[i][1](rd)
+        for got, ref in ((got_a, ref_a), (got_m, ref_m)):
+            max_abs, max_ulp, mean_ulp = _ulp_report(got.cpu(), ref, torch.bfloat16)
+            worst = max(worst, max_ulp)
+            # a value that sits next to zero has a tiny ulp: bound those by the absolute rounding noise of the block
+            far = ((got.cpu().float() - ref.float()).abs() > ulp_tolerance(ref, torch.bfloat16, limit, floor=2e-2 if fold else 4e-3))
+            assert not far.any(), (i, max_abs, max_ulp, mean_ulp)
+        x = ref_m
+    print(f"bf16 teacher-forced blocks (fold={fold}): worst {worst:.2f} ulp")
+
+
+def test_gpt2_xl_full_depth_bf16_vs_oracle():
+    """GPT-2 XL at its full depth (48 layers, h=1600, 25 heads of 64), bf16, 1 x 64 tokens (the CPU oracle's cost
+    is linear in tokens): free-running hidden state and logits against the oracle, reported as max-abs and in bf16
+    ulps; argmax equal wherever the oracle's top-2 margin exceeds two ulps."""
+    kw = dict(vocab_size=50257, block_size=1024, n_layer=48, n_head=25, n_embd=1600, dropout=0.1)
+    model, cfg, sd = build_model(kw, torch.bfloat16)
+    ids = torch.randint(0, 50257, (1, 64), generator=torch.Generator().manual_seed(0))
+    hidden = model(ids.to(DEV))
+    logits, next_ids = model.lm_head(hidden, return_argmax=True)
+    ref_hidden = orc.gpt_forward(sd, cfg, ids)
+    ref_logits = orc.lm_head(sd, ref_hidden)
+    h_abs, h_ulp, h_mean = _ulp_report(hidden.cpu(), ref_hidden, torch.bfloat16)
+    l_abs, l_ulp, l_mean = _ulp_report(logits.cpu(), ref_logits, torch.bfloat16)
+    print(f"XL 48 layers bf16: hidden max-abs {h_abs:.3g} (mean {h_mean:.2f} ulp), logits max-abs {l_abs:.3g} (mean {l_mean:.2f} ulp)")
+    assert h_abs < 0.5 and (hidden.cpu().float() - ref_hidden.float()).abs().mean().item() < 0.03
+    assert l_abs < 0.25 and (logits.cpu().float() - ref_logits.float()).abs().mean().item() < 0.02
+    _argmax_agrees_where_clear(logits.cpu(), ref_logits, 6.25e-2)
+    assert torch.equal(logits.gather(2, next_ids[..., None])[..., 0], logits.max(dim=-1).values)
+
+
+def test_weights_reloaded_after_a_forward_are_used():
+    """Packed and folded operands are cached per parameter version: a load_state_dict (or copy_) after the model
+    has already run must show up in the next forward, eager and graph-replayed; writes through param.data are
+    invisible to torch's version counters and need refresh_operands()."""
+    from gpt_triton_b200.gpt import FusedGPT, GPTConfig, GraphedForward
+
+    model, cfg, sd = build_model(TINY, torch.float16, random_affine=True)
+    ids = torch.randint(0, 1024, (2, 64), generator=torch.Generator().manual_seed(4)).to(DEV)
+    first = model.logits(ids).clone()
+    graphed = GraphedForward(model, ids, what="logits")
+    assert torch.equal(graphed(ids), first)
+    sd2 = orc.seeded_state_dict(cfg, seed=1, random_affine=True)
+    fresh = FusedGPT(GPTConfig(**TINY))
+    fresh.load_state_dict(sd2)
+    fresh = fresh.half().to(DEV).eval()
+    expect = fresh.logits(ids)
+    assert not torch.equal(expect, first)
+    model.load_state_dict({k: v.half() for k, v in sd2.items()})
+    assert torch.equal(model.logits(ids), expect)
+    assert torch.equal(graphed(ids), expect)  # re-captured: the old graph held the old packed weights
+    with torch.no_grad():
+        for prm in model.parameters():
+            prm.data.mul_(0.5)
+        for prm in fresh.parameters():
+            prm.mul_(0.5)
+    model.refresh_operands()
+    assert torch.equal(model.logits(ids), fresh.logits(ids))
 
 
 def test_cuda_graph_replay_matches_eager():

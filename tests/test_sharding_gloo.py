@@ -51,6 +51,18 @@ def _worker(rank, world, port, n_rows, out_dir):
         assert torch.equal(got, full)
         got = sharded_forward(_fake_logits, ids, gather="none")
         assert torch.equal(got, full[lo:hi])
+        # a callable that already returns ids (the fused lm_head epilogue on a GPU): gathered as they are
+        got = sharded_forward(lambda x: _fake_logits(x).argmax(-1), ids, gather="argmax", fn_returns="ids")
+        assert torch.equal(got, full.argmax(-1))
+        with pytest.raises(ValueError):
+            sharded_forward(_fake_logits, ids, gather="logits", fn_returns="ids")
+        if n_rows % world == 0:
+            from gpt_triton_b200.sharding import gather_equal_rows
+
+            out = torch.empty((n_rows, 6), dtype=ids.dtype)
+            assert gather_equal_rows(ids[lo:hi], out=out) is out and torch.equal(out, ids)
+            with pytest.raises(ValueError):
+                gather_equal_rows(ids[lo:hi], out=torch.empty((n_rows + 1, 6), dtype=ids.dtype))
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
