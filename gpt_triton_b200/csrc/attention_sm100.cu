@@ -3,21 +3,22 @@
 // reference, and both operands of one MMA must have the same format, so a bf16 V tile is converted to
 // fp16 in place (exact in fp16's normal range) by the softmax warps before P V.
 //
-// Work item = 128 query rows of one (batch, head).  Persistent CTAs (three per SM) walk the items,
+// Work item = 128 query rows of one (batch, head).  Persistent CTAs (two per SM) walk the items,
 // longest first.  Per CTA:
-//   warp 0      TMA producer: the 128x64 Q tile and, per 64-key block, the K and V tiles (2-stage ring),
-//               all 128-byte swizzled, straight out of the strided q/k/v views (4-D tensor maps:
-//               head_dim, row, head, batch); every CTA issues its own loads
-//   warp 1      tcgen05.mma issuer: S = Q K^T (128x64, fp32, tensor memory) and O (+)= P V, which
-//               accumulates in tensor memory over the key blocks of an item
-//   warps 2-5   softmax: one thread per query row.  Reads S from tensor memory, keeps the running
-//               maximum/denominator in fp32, writes P = exp(s - max) rounded to fp16 into shared
-//               memory in the swizzled K-major operand layout and, when the running maximum of any of
-//               its rows moved, rescales its 32 rows of O in tensor memory (load, multiply, store)
-//               before P V of the block is issued:  o = o * exp(m_old - m_new) + P V.
-// The output row never lives in registers across blocks, which keeps a softmax thread near 100
-// registers: three CTAs (twelve softmax warps) fit an SM, and it is the number of softmax warps in
-// flight that keeps the special-function unit, the limiter of attention at head size 64, busy.
+//   warp 0      TMA producer: the 128x64 Q tile (double-buffered) and, per 64-key block, the K and V tiles
+//               (3-stage ring), all 128-byte swizzled, straight out of the strided q/k/v views (4-D tensor
+//               maps: head_dim, row, head, batch); every CTA issues its own loads
+//   warp 1      tcgen05.mma issuer: S = Q K^T (128x64, fp32, tensor memory, double-buffered, issued one
+//               block ahead) and O (+)= P V, which accumulates in tensor memory over the key blocks of an item
+//   warps 2-5   softmax: one thread per query row.  Loads the row's 64 scores from tensor memory ONCE and keeps
+//               them in registers for both the block maximum and the exponentials (S is handed back to the
+//               tensor cores as soon as the load has landed), keeps the running maximum/denominator in fp32,
+//               writes P = exp(s - max) rounded to fp16 into shared memory in the swizzled K-major operand
+//               layout and, when the running maximum of any of its rows moved, rescales its 32 rows of O in
+//               tensor memory (load, multiply, store) before P V of the block is issued:
+//               o = o * exp(m_old - m_new) + P V.
+// The output row never lives in registers across blocks; that is what leaves room for the 64 scores, and a
+// softmax thread makes two round trips to tensor memory per block (scores; output rescale) instead of four.
 // The softmax runs over 64-key blocks with P rounded relative to the running maximum of each
 // block, which is the arithmetic of the reference's flash_attention_v1 kernel (kernels.py:417-474
 // of the reference); blocks above the diagonal are skipped.  Every mbarrier wait is bounded.
@@ -33,16 +34,16 @@ using namespace sm100;
 constexpr int D = 64;
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_N = 64;
-constexpr int KV_STAGES = 2;
+constexpr int KV_STAGES = 3;
 constexpr int Q_BYTES = BLOCK_M * D * 2;        // 16 KB
 constexpr int KV_TILE_BYTES = BLOCK_N * D * 2;  // 8 KB each for K and V
 constexpr int KV_STAGE_BYTES = 2 * KV_TILE_BYTES;
 constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;  // 16 KB
 constexpr int NUM_THREADS = 192;
-constexpr int CTAS_PER_SM = 3;
-constexpr int TMEM_COLS = 128;  // S (64 columns) + O (64 columns)
+constexpr int CTAS_PER_SM = 2;
+constexpr int TMEM_COLS = 256;  // S[2] (64 columns each) + O (64 columns); allocations are powers of two
 constexpr int CTRL_BYTES = 256;
-constexpr int SMEM_BYTES = Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES + 1024 + CTRL_BYTES;
+constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES + 1024 + CTRL_BYTES;
 
 struct Params {
   void* out;
@@ -143,20 +144,20 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  const uint32_t smem_q = base;                                  // [128][64]
-  const uint32_t smem_kv = smem_q + Q_BYTES;                     // [KV_STAGES]{K[64][64], V[64][64]}
+  const uint32_t smem_q = base;                                  // [2][128][64]
+  const uint32_t smem_kv = smem_q + 2 * Q_BYTES;                 // [KV_STAGES]{K[64][64], V[64][64]}
   const uint32_t smem_p = smem_kv + KV_STAGES * KV_STAGE_BYTES;  // [128][64] fp16
-  uint8_t* ctrl = smem + Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES;
+  uint8_t* ctrl = smem + 2 * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES;
   const uint32_t bars = smem_u32(ctrl);
-  const uint32_t bar_q_full = bars;                             // Q tile of the current item has landed
-  const uint32_t bar_q_empty = bars + 8;                        // every S of the item has been computed: Q may be overwritten
-  const uint32_t bar_kv_full = bars + 16;                       // [KV_STAGES]
+  const uint32_t bar_q_full = bars;                             // [2] Q tile of an item has landed
+  const uint32_t bar_q_empty = bars + 16;                       // [2] every S of the item has been computed: the buffer may be overwritten
+  const uint32_t bar_kv_full = bars + 32;                       // [KV_STAGES]
   const uint32_t bar_kv_empty = bar_kv_full + 8 * KV_STAGES;    // [KV_STAGES]
-  const uint32_t bar_s_full = bar_kv_empty + 8 * KV_STAGES;     // S of a block is in tensor memory
-  const uint32_t bar_s_empty = bar_s_full + 8;                  // the four softmax warps have read it
-  const uint32_t bar_p_full = bar_s_empty + 8;                  // P of a block is in shared memory and O has been rescaled
+  const uint32_t bar_s_full = bar_kv_empty + 8 * KV_STAGES;     // [2] S of a block is in tensor memory
+  const uint32_t bar_s_empty = bar_s_full + 16;                 // [2] the four softmax warps hold its scores in registers
+  const uint32_t bar_p_full = bar_s_empty + 16;                 // P of a block is in shared memory and O has been rescaled
   const uint32_t bar_pv_done = bar_p_full + 8;                  // P V of a block has been accumulated: P is free, O is current
-  constexpr int BAR_BYTES = 16 + 16 * KV_STAGES + 32;
+  constexpr int BAR_BYTES = 32 + 16 * KV_STAGES + 32 + 16;
   static_assert(BAR_BYTES + 16 <= CTRL_BYTES, "control block too small");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + BAR_BYTES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + BAR_BYTES + 8);
@@ -167,14 +168,16 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int64_t n_items = (int64_t)n_qt * bh_total;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_q_full, 1);
-    mbar_init(bar_q_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_q_full + 8 * i, 1);
+      mbar_init(bar_q_empty + 8 * i, 1);
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_s_empty + 8 * i, 4);
+    }
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(bar_kv_full + 8 * i, 1);
       mbar_init(bar_kv_empty + 8 * i, 1);
     }
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_s_empty, 4);
     mbar_init(bar_p_full, 4);
     mbar_init(bar_pv_done, 1);
     *abort_flag = 0;
@@ -192,8 +195,8 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // set-up done (own shared and tensor memory only); global memory from here on
   pdl_launch_dependents();
   pdl_wait();
-  const uint32_t tmem_s = tmem_base;            // S: columns [0, 64)
-  const uint32_t tmem_o = tmem_base + BLOCK_N;  // O: columns [64, 128)
+  const uint32_t tmem_s = tmem_base;                // S[buf]: columns [64 * buf, 64 * buf + 64)
+  const uint32_t tmem_o = tmem_base + 2 * BLOCK_N;  // O: columns [128, 192)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -202,9 +205,10 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       bool alive = true;
       for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
         const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
-        if (!mbar_wait(bar_q_empty, (qi & 1) ^ 1u, abort_flag, p.status_word, 11)) break;
-        mbar_arrive_expect_tx(bar_q_full, Q_BYTES);
-        tma_load_4d(smem_q, &map_q, bar_q_full, 0, p.q_head_inner ? it.h : it.q0, p.q_head_inner ? it.q0 : it.h, it.b);
+        const uint32_t qb = qi & 1;
+        if (!mbar_wait(bar_q_empty + 8 * qb, ((qi >> 1) & 1) ^ 1u, abort_flag, p.status_word, 11)) break;
+        mbar_arrive_expect_tx(bar_q_full + 8 * qb, Q_BYTES);
+        tma_load_4d(smem_q + qb * Q_BYTES, &map_q, bar_q_full + 8 * qb, 0, p.q_head_inner ? it.h : it.q0, p.q_head_inner ? it.q0 : it.h, it.b);
         ++qi;
         for (int j = 0; j < it.nblk; ++j) {
           const uint32_t st = ki % KV_STAGES;
@@ -224,33 +228,35 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       uint32_t qi = 0, ks = 0, kp = 0, si = 0, pi = 0;
       bool alive = true;
-      // S_next = Q . K^T: needs the block's K/V stage and the softmax warps to be done with the previous S
-      auto issue_s = [&]() -> bool {
+      // S_next = Q . K^T into S[si & 1]: needs the block's K/V stage and that buffer's previous scores to be in registers
+      auto issue_s = [&](uint32_t qb) -> bool {
         const uint32_t st = ks % KV_STAGES;
         if (!mbar_wait(bar_kv_full + 8 * st, (ks / KV_STAGES) & 1, abort_flag, p.status_word, 13)) return false;
-        if (!mbar_wait(bar_s_empty, (si & 1) ^ 1u, abort_flag, p.status_word, 14)) return false;
+        const uint32_t sb = si & 1;
+        if (!mbar_wait(bar_s_empty + 8 * sb, ((si >> 1) & 1) ^ 1u, abort_flag, p.status_word, 14)) return false;
         tc_fence_after();
-        const uint64_t da = desc_kmajor(smem_q);
+        const uint64_t da = desc_kmajor(smem_q + qb * Q_BYTES);
         const uint64_t db = desc_kmajor(smem_kv + st * KV_STAGE_BYTES);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc_s, (uint32_t)(k != 0));
-        umma_commit(bar_s_full);
+        for (int k = 0; k < D / 16; ++k) umma_f16(tmem_s + sb * BLOCK_N, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc_s, (uint32_t)(k != 0));
+        umma_commit(bar_s_full + 8 * sb);
         ++si;
         ++ks;
         return true;
       };
       for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
         const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
-        if (!mbar_wait(bar_q_full, qi & 1, abort_flag, p.status_word, 15)) break;
-        if (!issue_s()) break;
+        const uint32_t qb = qi & 1;
+        if (!mbar_wait(bar_q_full + 8 * qb, (qi >> 1) & 1, abort_flag, p.status_word, 15)) break;
+        if (!issue_s(qb)) break;
         for (int j = 0; j < it.nblk; ++j) {
           if (j + 1 < it.nblk) {
-            if (!issue_s()) {
+            if (!issue_s(qb)) {
               alive = false;
               break;
             }
           } else {
-            umma_commit(bar_q_empty);  // every S of this item is issued: Q is free once they finish
+            umma_commit(bar_q_empty + 8 * qb);  // every S of this item is issued: Q is free once they finish
           }
           // O (+)= P_j . V_j : P written, O rescaled (and, for bf16 storage, V converted) by the softmax warps
           const uint32_t st = kp % KV_STAGES;
@@ -281,7 +287,6 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t p_row = smem_p + (uint32_t)r_in_tile * 128u;
     const uint32_t sw = (uint32_t)(r_in_tile & 7);
-    const uint32_t s_addr = tmem_s + lane_addr;
     const uint32_t o_addr = tmem_o + lane_addr;
     uint32_t it_count = 0;  // 64-key blocks processed so far by this CTA
     bool alive = true;
@@ -292,30 +297,53 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool warp_live = warp_row0 < p.L;           // a warp whose 32 rows all lie beyond L only keeps the handshakes going
       float m_run = -INFINITY, l_run = 0.f;
       for (int j = 0; j < it.nblk; ++j, ++it_count) {
-        if (!mbar_wait(bar_s_full, it_count & 1, abort_flag, p.status_word, 18)) {
+        const uint32_t sb = it_count & 1;
+        if (!mbar_wait(bar_s_full + 8 * sb, (it_count >> 1) & 1, abort_flag, p.status_word, 18)) {
           alive = false;
           break;
         }
         tc_fence_after();
+        const uint32_t s_addr = tmem_s + lane_addr + sb * BLOCK_N;
         const int k0 = j * BLOCK_N;
         // a 32-key chunk whose first key lies above this warp's last row is masked for the whole warp
         const int live_chunks = (!warp_live || k0 > warp_row0 + 31) ? 0 : (k0 + 32 > warp_row0 + 31 ? 1 : 2);
-        // pass 1: block maximum of the raw scores (the scale is positive, so it commutes with max).  A 32-key
-        // chunk needs per-element masking only if the diagonal crosses it for some row of this warp.
+        // the row's scores, loaded once: both 32-column loads in flight under a single wait
+        uint32_t v0[32], v1[32];
+        if (live_chunks > 0) tmem_ld_32x32(s_addr, v0);
+        if (live_chunks > 1) tmem_ld_32x32(s_addr + 32, v1);
+        if (live_chunks > 0) tmem_ld_wait();
+        // S[sb] is in registers: the Q K^T after next may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_s_empty + 8 * sb);
+        // block maximum of the raw scores (the scale is positive, so it commutes with max).  A 32-key chunk needs
+        // per-element masking only if the diagonal crosses it for some row of this warp; masked scores become -inf
+        // here, so that the exponentials below need no second test.
         float bm = -INFINITY;
+        if (live_chunks > 0) {
+          if (k0 + 31 > warp_row0) {
+            const int lim = row - k0;  // keys i <= lim are visible to this row
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          if (c >= live_chunks) break;
-          uint32_t v[32];
-          tmem_ld_32x32(s_addr + c * 32, v);
-          tmem_ld_wait();
-          if (k0 + c * 32 + 31 > warp_row0) {
-            const int lim = row - k0 - c * 32;  // keys i <= lim are visible to this row
-#pragma unroll
-            for (int i = 0; i < 32; ++i) bm = fmaxf(bm, i > lim ? -INFINITY : __uint_as_float(v[i]));
+            for (int i = 0; i < 32; ++i) {
+              if (i > lim) v0[i] = 0xff800000u;
+              bm = fmaxf(bm, __uint_as_float(v0[i]));
+            }
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) bm = fmax3(bm, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+            for (int i = 0; i < 32; i += 2) bm = fmax3(bm, __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]));
+          }
+        }
+        if (live_chunks > 1) {
+          if (k0 + 63 > warp_row0) {
+            const int lim = row - k0 - 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i > lim) v1[i] = 0xff800000u;
+              bm = fmaxf(bm, __uint_as_float(v1[i]));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) bm = fmax3(bm, __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]));
           }
         }
         const float m_new = fmaxf(m_run, bm * p.scale_log2e);  // running maximum, in log2 units
@@ -328,7 +356,8 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           alive = false;
           break;
         }
-        // pass 2: p = exp(s - max), row sum in fp32, P rounded to fp16 into the swizzled operand tile
+        // p = exp(s - max) from the registers, row sum in fp32, P rounded to fp16 into the swizzled operand tile
+        // (a masked score is -inf: 2^-inf = 0; a row with nothing visible yet has max = -inf and is never stored)
         float psum = 0.f;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -340,31 +369,15 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             continue;
           }
-          uint32_t v[32];
-          tmem_ld_32x32(s_addr + c * 32, v);
-          tmem_ld_wait();
+          const uint32_t(&v)[32] = c == 0 ? v0 : v1;
           uint32_t w[16];
-          if (k0 + c * 32 + 31 > warp_row0) {
-            const int lim = row - k0 - c * 32;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float x0 = fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new);
-              const float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m_new);
-              const float p0 = i > lim ? 0.f : ex2f(x0);
-              const float p1 = i + 1 > lim ? 0.f : ex2f(x1);
-              psum += p0 + p1;
-              __half2 h = __floats2half2_rn(p0, p1);
-              w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float p0 = ex2f(fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new));
-              const float p1 = ex2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m_new));
-              psum += p0 + p1;
-              __half2 h = __floats2half2_rn(p0, p1);
-              w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
-            }
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2f(fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new));
+            const float p1 = ex2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m_new));
+            psum += p0 + p1;
+            __half2 h = __floats2half2_rn(p0, p1);
+            w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
           }
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -372,10 +385,6 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             st_shared_v4(p_row + ((chunk ^ sw) << 4), w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
           }
         }
-        // S has been read: the next block's Q K^T may overwrite it
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_s_empty);
         if constexpr (sizeof(T) == 2 && !IS_FP16) {
           // bf16 storage: V_j -> fp16 in place, 64 bytes per softmax thread (the swizzle is address-agnostic)
           const uint32_t vaddr = smem_kv + (it_count % KV_STAGES) * KV_STAGE_BYTES + KV_TILE_BYTES + (uint32_t)(threadIdx.x - 64) * 64u;
@@ -394,15 +403,17 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         // o = o * exp(m_old - m_new) in tensor memory, for this warp's 32 rows, unless no row's maximum moved
         if (j > 0 && warp_live && __any_sync(0xffffffffu, mult != 1.0f)) {
+          uint32_t a0[32], a1[32];
+          tmem_ld_32x32(o_addr, a0);
+          tmem_ld_32x32(o_addr + 32, a1);
+          tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(o_addr + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * mult);
-            tmem_st_32x32(o_addr + c * 32, v);
+          for (int i = 0; i < 32; ++i) {
+            a0[i] = __float_as_uint(__uint_as_float(a0[i]) * mult);
+            a1[i] = __float_as_uint(__uint_as_float(a1[i]) * mult);
           }
+          tmem_st_32x32(o_addr, a0);
+          tmem_st_32x32(o_addr + 32, a1);
           tmem_st_wait();
         }
         // P (and, for bf16, the converted V) is complete, O is rescaled: P V of this block may be issued
@@ -419,11 +430,13 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (warp_live) {  // (warp-uniform: the tensor-memory loads below are warp-wide instructions)
         const float inv = 1.0f / l_run;
         T* dst = reinterpret_cast<T*>(p.out) + (int64_t)it.b * p.so_b + (int64_t)it.h * p.so_h + (int64_t)row * p.so_l;
+        uint32_t a0[32], a1[32];
+        tmem_ld_32x32(o_addr, a0);
+        tmem_ld_32x32(o_addr + 32, a1);
+        tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(o_addr + c * 32, v);
-          tmem_ld_wait();
+          const uint32_t(&v)[32] = c == 0 ? a0 : a1;
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) w[i] = pack_out<T>(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
