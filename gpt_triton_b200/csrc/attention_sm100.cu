@@ -10,15 +10,19 @@
 //               maps: head_dim, row, head, batch); every CTA issues its own loads
 //   warp 1      tcgen05.mma issuer: S = Q K^T (128x64, fp32, tensor memory, double-buffered, issued one
 //               block ahead) and O (+)= P V, which accumulates in tensor memory over the key blocks of an item
-//   warps 2-5   softmax: one thread per query row.  Loads the row's 64 scores from tensor memory ONCE and keeps
-//               them in registers for both the block maximum and the exponentials (S is handed back to the
-//               tensor cores as soon as the load has landed), keeps the running maximum/denominator in fp32,
-//               writes P = exp(s - max) rounded to fp16 into shared memory in the swizzled K-major operand
-//               layout and, when the running maximum of any of its rows moved, rescales its 32 rows of O in
+//   warps 2-9   softmax: TWO threads per query row (warps w and w + 4 own the same 32 rows; each takes 32 of the
+//               block's 64 keys and 32 of the 64 output columns).  A thread loads its 32 scores from tensor memory
+//               ONCE and keeps them in registers for both the block maximum and the exponentials (S is handed
+//               back to the tensor cores as soon as the load has landed); the two halves of a row exchange their
+//               block maxima through shared memory; running maximum/denominator in fp32; P = exp(s - max)
+//               rounded to fp16 goes into shared memory in the swizzled K-major operand layout and, when the
+//               running maximum of any row of the warp moved, the warp rescales its 32 rows x 32 columns of O in
 //               tensor memory (load, multiply, store) before P V of the block is issued:
 //               o = o * exp(m_old - m_new) + P V.
-// The output row never lives in registers across blocks; that is what leaves room for the 64 scores, and a
-// softmax thread makes two round trips to tensor memory per block (scores; output rescale) instead of four.
+// The output row never lives in registers across blocks, and a softmax thread makes two round trips to tensor
+// memory per block (scores; output rescale).  The work of a row is serial in its thread (exponentials at one warp
+// instruction per 8 cycles on the special-function unit, dependent arithmetic, barrier hand-offs); two threads per
+// row halve that chain and double the warps the SM can interleave.
 // The softmax runs over 64-key blocks with P rounded relative to the running maximum of each
 // block, which is the arithmetic of the reference's flash_attention_v1 kernel (kernels.py:417-474
 // of the reference); blocks above the diagonal are skipped.  Every mbarrier wait is bounded.
@@ -39,11 +43,13 @@ constexpr int Q_BYTES = BLOCK_M * D * 2;        // 16 KB
 constexpr int KV_TILE_BYTES = BLOCK_N * D * 2;  // 8 KB each for K and V
 constexpr int KV_STAGE_BYTES = 2 * KV_TILE_BYTES;
 constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;  // 16 KB
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_SOFTMAX_WARPS = 8;  // two threads per query row: warps w and w + 4 share a 32-row quarter, 32 keys each
+constexpr int NUM_THREADS = 32 * (2 + NUM_SOFTMAX_WARPS);
 constexpr int CTAS_PER_SM = 2;
 constexpr int TMEM_COLS = 256;  // S[2] (64 columns each) + O (64 columns); allocations are powers of two
 constexpr int CTRL_BYTES = 256;
-constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES + 1024 + CTRL_BYTES;
+constexpr int XCHG_BYTES = 3 * 2 * BLOCK_M * 4;  // [slot][half][row]: block maximum / row sum of each half of a row, for its partner thread
+constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + P_BYTES + 1024 + CTRL_BYTES + XCHG_BYTES;
 
 struct Params {
   void* out;
@@ -157,10 +163,12 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t bar_s_empty = bar_s_full + 16;                 // [2] the four softmax warps hold its scores in registers
   const uint32_t bar_p_full = bar_s_empty + 16;                 // P of a block is in shared memory and O has been rescaled
   const uint32_t bar_pv_done = bar_p_full + 8;                  // P V of a block has been accumulated: P is free, O is current
-  constexpr int BAR_BYTES = 32 + 16 * KV_STAGES + 32 + 16;
+  const uint32_t bar_pair = bar_pv_done + 8;                    // [4] the two warps that share a 32-row quarter have published their halves
+  constexpr int BAR_BYTES = 32 + 16 * KV_STAGES + 32 + 16 + 32;
   static_assert(BAR_BYTES + 16 <= CTRL_BYTES, "control block too small");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + BAR_BYTES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + BAR_BYTES + 8);
+  float* xchg = reinterpret_cast<float*>(ctrl + CTRL_BYTES);  // [2][128]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.L + BLOCK_M - 1) / BLOCK_M;
@@ -172,14 +180,15 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(bar_q_full + 8 * i, 1);
       mbar_init(bar_q_empty + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_s_empty + 8 * i, 4);
+      mbar_init(bar_s_empty + 8 * i, NUM_SOFTMAX_WARPS);
     }
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(bar_kv_full + 8 * i, 1);
       mbar_init(bar_kv_empty + 8 * i, 1);
     }
-    mbar_init(bar_p_full, 4);
+    mbar_init(bar_p_full, NUM_SOFTMAX_WARPS);
     mbar_init(bar_pv_done, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(bar_pair + 8 * i, 2);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async_smem();
@@ -281,13 +290,30 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax warps: one thread per query row
-    const int quarter = warp & 3;
+    // ------------------------------------------------------------ softmax warps: two threads per query row
+    const int quarter = warp & 3;               // tensor-memory lanes [32 * quarter, +32) are this warp's rows
+    const int half = (warp - 2) >> 2;           // which 32 of a block's 64 keys / of the 64 output columns
     const int r_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t p_row = smem_p + (uint32_t)r_in_tile * 128u;
     const uint32_t sw = (uint32_t)(r_in_tile & 7);
-    const uint32_t o_addr = tmem_o + lane_addr;
+    const uint32_t o_addr = tmem_o + lane_addr + (uint32_t)(half * 32);
+    // Exchange between the two threads of a row: slot layout [3][2][128] floats.  Block exchanges alternate between
+    // slots 0 and 1 (a thread can only be one exchange ahead of its partner), the end-of-item exchange uses slot 2.
+    float* my_x = xchg + half * BLOCK_M + r_in_tile;
+    const float* partner_x = xchg + (half ^ 1) * BLOCK_M + r_in_tile;
+    const uint32_t my_pair_bar = bar_pair + 8 * (uint32_t)quarter;
+    uint32_t xphase = 0;
+    // publish `val` for the partner, wait (bounded) for the partner's, return it; false when the CTA is aborting
+    auto exchange = [&](int slot, float val, float& other) -> bool {
+      my_x[slot * 2 * BLOCK_M] = val;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_pair_bar);
+      if (!mbar_wait(my_pair_bar, xphase, abort_flag, p.status_word, 22)) return false;
+      xphase ^= 1u;
+      other = partner_x[slot * 2 * BLOCK_M];
+      return true;
+    };
     uint32_t it_count = 0;  // 64-key blocks processed so far by this CTA
     bool alive = true;
     for (int64_t idx = blockIdx.x; idx < n_items && alive; idx += gridDim.x) {
@@ -295,7 +321,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int row = it.q0 + r_in_tile;
       const int warp_row0 = it.q0 + quarter * 32;       // first query row of this warp
       const bool warp_live = warp_row0 < p.L;           // a warp whose 32 rows all lie beyond L only keeps the handshakes going
-      float m_run = -INFINITY, l_run = 0.f;
+      float m_run = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row's denominator
       for (int j = 0; j < it.nblk; ++j, ++it_count) {
         const uint32_t sb = it_count & 1;
         if (!mbar_wait(bar_s_full + 8 * sb, (it_count >> 1) & 1, abort_flag, p.status_word, 18)) {
@@ -303,49 +329,47 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           break;
         }
         tc_fence_after();
-        const uint32_t s_addr = tmem_s + lane_addr + sb * BLOCK_N;
-        const int k0 = j * BLOCK_N;
-        // a 32-key chunk whose first key lies above this warp's last row is masked for the whole warp
-        const int live_chunks = (!warp_live || k0 > warp_row0 + 31) ? 0 : (k0 + 32 > warp_row0 + 31 ? 1 : 2);
-        // the row's scores, loaded once: both 32-column loads in flight under a single wait
-        uint32_t v0[32], v1[32];
-        if (live_chunks > 0) tmem_ld_32x32(s_addr, v0);
-        if (live_chunks > 1) tmem_ld_32x32(s_addr + 32, v1);
-        if (live_chunks > 0) tmem_ld_wait();
+        const int k0 = j * BLOCK_N + half * 32;  // first key of this thread's 32
+        // keys above this warp's last row are masked for the whole warp
+        const bool live = warp_live && k0 <= warp_row0 + 31;
+        uint32_t v[32];
+        if (live) {
+          tmem_ld_32x32(tmem_s + lane_addr + sb * BLOCK_N + (uint32_t)(half * 32), v);
+          tmem_ld_wait();
+        }
         // S[sb] is in registers: the Q K^T after next may overwrite it
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_s_empty + 8 * sb);
-        // block maximum of the raw scores (the scale is positive, so it commutes with max).  A 32-key chunk needs
-        // per-element masking only if the diagonal crosses it for some row of this warp; masked scores become -inf
-        // here, so that the exponentials below need no second test.
+        // maximum of the raw scores (the scale is positive, so it commutes with max).  Per-element masking only if the
+        // diagonal crosses these 32 keys for some row of this warp; masked scores become -inf here, so that the
+        // exponentials below need no second test.
         float bm = -INFINITY;
-        if (live_chunks > 0) {
+        if (live) {
           if (k0 + 31 > warp_row0) {
             const int lim = row - k0;  // keys i <= lim are visible to this row
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              if (i > lim) v0[i] = 0xff800000u;
-              bm = fmaxf(bm, __uint_as_float(v0[i]));
+              if (i > lim) v[i] = 0xff800000u;
+              bm = fmaxf(bm, __uint_as_float(v[i]));
             }
           } else {
+            float b1 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) bm = fmax3(bm, __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]));
-          }
-        }
-        if (live_chunks > 1) {
-          if (k0 + 63 > warp_row0) {
-            const int lim = row - k0 - 32;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (i > lim) v1[i] = 0xff800000u;
-              bm = fmaxf(bm, __uint_as_float(v1[i]));
+            for (int i = 0; i < 32; i += 4) {
+              bm = fmax3(bm, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+              b1 = fmax3(b1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) bm = fmax3(bm, __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]));
+            bm = fmaxf(bm, b1);
           }
         }
+        // the row's block maximum is the larger of its two halves
+        float partner_bm;
+        if (!exchange((int)(it_count & 1), bm, partner_bm)) {
+          alive = false;
+          break;
+        }
+        bm = fmaxf(bm, partner_bm);
         const float m_new = fmaxf(m_run, bm * p.scale_log2e);  // running maximum, in log2 units
         const float mult = ex2f(m_run - m_new);
         m_run = m_new;
@@ -356,40 +380,36 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           alive = false;
           break;
         }
-        // p = exp(s - max) from the registers, row sum in fp32, P rounded to fp16 into the swizzled operand tile
+        tc_fence_after();
+        // p = exp(s - max) from the registers, partial row sum in fp32, P rounded to fp16 into the swizzled operand tile
         // (a masked score is -inf: 2^-inf = 0; a row with nothing visible yet has max = -inf and is never stored)
-        float psum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          if (c >= live_chunks) {
-            // masked for every row of the warp: P = 0 (rows beyond L may keep whatever is there: nothing reads their output)
-            if (warp_live) {
-#pragma unroll
-              for (int g = 0; g < 4; ++g) st_shared_v4(p_row + ((((uint32_t)(c * 4 + g)) ^ sw) << 4), 0u, 0u, 0u, 0u);
-            }
-            continue;
-          }
-          const uint32_t(&v)[32] = c == 0 ? v0 : v1;
+        float psum0 = 0.f, psum1 = 0.f;
+        if (live) {
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const float p0 = ex2f(fmaf(__uint_as_float(v[i]), p.scale_log2e, -m_new));
             const float p1 = ex2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -m_new));
-            psum += p0 + p1;
+            psum0 += p0;
+            psum1 += p1;
             __half2 h = __floats2half2_rn(p0, p1);
             w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
           }
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const uint32_t chunk = (uint32_t)(c * 4 + g);
+            const uint32_t chunk = (uint32_t)(half * 4 + g);
             st_shared_v4(p_row + ((chunk ^ sw) << 4), w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
           }
+        } else if (warp_live) {
+          // masked for every row of the warp: P = 0 (rows beyond L may keep whatever is there: nothing reads their output)
+#pragma unroll
+          for (int g = 0; g < 4; ++g) st_shared_v4(p_row + ((((uint32_t)(half * 4 + g)) ^ sw) << 4), 0u, 0u, 0u, 0u);
         }
         if constexpr (sizeof(T) == 2 && !IS_FP16) {
-          // bf16 storage: V_j -> fp16 in place, 64 bytes per softmax thread (the swizzle is address-agnostic)
-          const uint32_t vaddr = smem_kv + (it_count % KV_STAGES) * KV_STAGE_BYTES + KV_TILE_BYTES + (uint32_t)(threadIdx.x - 64) * 64u;
+          // bf16 storage: V_j -> fp16 in place, 32 bytes per softmax thread (the swizzle is address-agnostic)
+          const uint32_t vaddr = smem_kv + (it_count % KV_STAGES) * KV_STAGE_BYTES + KV_TILE_BYTES + (uint32_t)(threadIdx.x - 64) * 32u;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < 2; ++g) {
             uint32_t w4[4];
             ld_shared_v4(vaddr + g * 16, w4);
 #pragma unroll
@@ -401,19 +421,14 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             st_shared_v4(vaddr + g * 16, w4[0], w4[1], w4[2], w4[3]);
           }
         }
-        // o = o * exp(m_old - m_new) in tensor memory, for this warp's 32 rows, unless no row's maximum moved
+        // o = o * exp(m_old - m_new) in tensor memory, for this warp's 32 rows x 32 columns, unless no row's maximum moved
         if (j > 0 && warp_live && __any_sync(0xffffffffu, mult != 1.0f)) {
-          uint32_t a0[32], a1[32];
-          tmem_ld_32x32(o_addr, a0);
-          tmem_ld_32x32(o_addr + 32, a1);
+          uint32_t a[32];
+          tmem_ld_32x32(o_addr, a);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            a0[i] = __float_as_uint(__uint_as_float(a0[i]) * mult);
-            a1[i] = __float_as_uint(__uint_as_float(a1[i]) * mult);
-          }
-          tmem_st_32x32(o_addr, a0);
-          tmem_st_32x32(o_addr + 32, a1);
+          for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * mult);
+          tmem_st_32x32(o_addr, a);
           tmem_st_wait();
         }
         // P (and, for bf16, the converted V) is complete, O is rescaled: P V of this block may be issued
@@ -421,33 +436,32 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_p_full);
-        l_run = l_run * mult + psum;
+        l_run = l_run * mult + (psum0 + psum1);
       }
       if (!alive) break;
-      // the last block's P V, then normalise and store the row
+      // the row's denominator is the sum of its two halves (the same rescale factors went into both)
+      float partner_l;
+      if (!exchange(2, l_run, partner_l)) break;
+      const float l_row = l_run + partner_l;
+      // the last block's P V, then normalise and store this thread's 32 output columns of the row
       if (!mbar_wait(bar_pv_done, (it_count - 1) & 1, abort_flag, p.status_word, 21)) break;
       tc_fence_after();
-      if (warp_live) {  // (warp-uniform: the tensor-memory loads below are warp-wide instructions)
-        const float inv = 1.0f / l_run;
-        T* dst = reinterpret_cast<T*>(p.out) + (int64_t)it.b * p.so_b + (int64_t)it.h * p.so_h + (int64_t)row * p.so_l;
-        uint32_t a0[32], a1[32];
-        tmem_ld_32x32(o_addr, a0);
-        tmem_ld_32x32(o_addr + 32, a1);
+      if (warp_live) {  // (warp-uniform: the tensor-memory load below is a warp-wide instruction)
+        const float inv = 1.0f / l_row;
+        T* dst = reinterpret_cast<T*>(p.out) + (int64_t)it.b * p.so_b + (int64_t)it.h * p.so_h + (int64_t)row * p.so_l + half * 32;
+        uint32_t a[32];
+        tmem_ld_32x32(o_addr, a);
         tmem_ld_wait();
+        uint32_t w[16];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const uint32_t(&v)[32] = c == 0 ? a0 : a1;
-          uint32_t w[16];
+        for (int i = 0; i < 16; ++i) w[i] = pack_out<T>(__uint_as_float(a[2 * i]) * inv, __uint_as_float(a[2 * i + 1]) * inv);
+        if (row < p.L) {
+          if (p.out_vec32) {
+            st_global_v8(dst, &w[0]);
+            st_global_v8(dst + 16, &w[8]);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) w[i] = pack_out<T>(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
-          if (row < p.L) {
-            if (p.out_vec32) {
-              st_global_v8(dst + c * 32, &w[0]);
-              st_global_v8(dst + c * 32 + 16, &w[8]);
-            } else {
-#pragma unroll
-              for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
-            }
+            for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
           }
         }
       }
