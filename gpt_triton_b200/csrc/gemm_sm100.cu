@@ -876,10 +876,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       if constexpr (STATS != 0 && sizeof(OutT) == 2) {
         if (stats.pending_col0 >= 0) {
-          // the winning chunk still sits in this warp's staging boxes (nothing overwrites them before the next tile)
-          const int c = (stats.pending_col0 - col_base) >> 5;
-          stats.best_idx = stats.pending_col0 + find_staged_column<OutT>((STATS == 3 ? stats_stage : stage_addr) + (uint32_t)(c >> 1) * EPI_BOX_BYTES,
-                                                                         c & 1, lane, stats.best_val);
+          if constexpr (STATS == 3) {
+            // nothing is stored: look the column up now; the winning chunk still sits in this warp's staging boxes
+            // (nothing overwrites them before the next tile)
+            const int c = (stats.pending_col0 - col_base) >> 5;
+            stats.best_idx = stats.pending_col0 + find_staged_column<OutT>(stats_stage + (uint32_t)(c >> 1) * EPI_BOX_BYTES, c & 1, lane, stats.best_val);
+          } else {
+            // the product is stored: only the 32-column chunk of the maximum is recorded here (as -(first column + 1));
+            // the reducing kernel reads those 32 stored values of the one chunk that wins the whole row
+            stats.best_idx = -(stats.pending_col0 + 1);
+          }
         }
       }
       if constexpr (LN == 2) {
@@ -1041,10 +1047,14 @@ static int launch_typed(const void* a, const void* b, const void* bias, const vo
 // covers 32 rows with 8 threads per row: thread (x, y) walks slices y, y + 8, ... of row x (32 consecutive rows of
 // one slice are one 128-byte line), then the 8 partial results of a row are merged through shared memory.  Strict
 // '>' within a thread and the lower column on equal values across threads keep the lowest column among equal maxima.
+// A partial's column is either exact (>= 0) or -(c0 + 1): "somewhere in the 32 stored columns starting at c0"; for the
+// row's winner that chunk of the stored product is read back and its first column equal to the maximum taken.
 constexpr int kReduceRows = 32, kReduceSplit = 8;
+__device__ __forceinline__ int partial_column(int enc) { return enc < 0 ? -enc - 1 : enc; }
 __global__ void __launch_bounds__(kReduceRows * kReduceSplit)
 argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx, const float* __restrict__ sum, int64_t ld, int slices,
-                     int64_t M, int64_t* __restrict__ out, float* __restrict__ lse_out) {
+                     int64_t M, int64_t* __restrict__ out, float* __restrict__ lse_out, const void* __restrict__ product, int64_t ld_product,
+                     int product_is_bf16, int64_t N) {
   __shared__ float s_val[kReduceSplit][kReduceRows];
   __shared__ int s_idx[kReduceSplit][kReduceRows];
   __shared__ float s_sum[kReduceSplit][kReduceRows];
@@ -1072,22 +1082,40 @@ argmax_reduce_kernel(const float* __restrict__ val, const int* __restrict__ idx,
       const float v = s_val[k][x];
       const int w = s_idx[k][x];
       const float t = s_sum[k][x];
-      if (v > best || (v == best && w < where)) {
+      if (v > best || (v == best && w != 0x7fffffff && (where == 0x7fffffff || partial_column(w) < partial_column(where)))) {
         total = total * (best > -INFINITY ? __expf(best - v) : 0.f) + t;
         best = v, where = w;
       } else if (v > -INFINITY) {
         total += t * __expf(v - best);
       }
     }
-    out[row] = where == 0x7fffffff ? 0 : where;
+    if (where == 0x7fffffff) {
+      where = 0;
+    } else if (where < 0) {
+      const int c0 = -where - 1;
+      where = c0;
+      if (product) {
+        for (int i = 0; i < 32 && c0 + i < N; ++i) {
+          const float pv = product_is_bf16 ? to_float(static_cast<const __nv_bfloat16*>(product)[row * ld_product + c0 + i])
+                                           : to_float(static_cast<const __half*>(product)[row * ld_product + c0 + i]);
+          if (pv == best) {
+            where = c0 + i;
+            break;
+          }
+        }
+      }
+    }
+    out[row] = where;
     if (lse_out) lse_out[row] = best + logf(total);
   }
 }
 
 static int launch_argmax_reduce(const float* val, const int* idx, const float* sum, int64_t ld, int slices, int64_t M, int64_t* out, float* lse_out,
-                                cudaStream_t stream) {
+                                const void* product, int64_t ld_product, int product_dtype, int64_t N, cudaStream_t stream) {
   LaunchSetup ls(dim3((unsigned)((M + kReduceRows - 1) / kReduceRows)), dim3(kReduceRows * kReduceSplit), 0, stream);
-  const cudaError_t e = cudaLaunchKernelEx(&ls.cfg, argmax_reduce_kernel, val, idx, sum, ld, slices, M, out, lse_out);
+  const int is_bf16 = product_dtype == B200_BF16;
+  if (product_dtype == B200_F32) product = nullptr;  // fp32 products never defer the column
+  const cudaError_t e = cudaLaunchKernelEx(&ls.cfg, argmax_reduce_kernel, val, idx, sum, ld, slices, M, out, lse_out, product, ld_product, is_bf16, N);
   note_launches(1);
   return status_from_cuda(e);
 }
@@ -1241,7 +1269,7 @@ int launch_gemm_argmax(const void* a, const void* b, const void* bias, const voi
 #undef B200_GEMM_DISPATCH
   if (st != B200_OK || !argmax_out) return st;
   const int64_t slices = (N + BN - 1) / BN * (BN / EPI_COLS);
-  return launch_argmax_reduce(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out, stream);
+  return launch_argmax_reduce(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out, out, ld_out, io_dtype, N, stream);
 }
 
 // Row statistics of A B^T (+ bias) without storing the product: argmax, log-sum-exp and, optionally, the value at a
@@ -1273,7 +1301,7 @@ int launch_gemm_rowstats(const void* a, const void* b, const void* bias, int64_t
   else
     st = launch_typed<__nv_bfloat16, false, 3>(a, b, bias, nullptr, nullptr, M, N, K, lda, ldb, 0, N, op_dtype, am, status_word, stream, targets, target_out);
   if (st != B200_OK) return st;
-  return launch_argmax_reduce(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out, stream);
+  return launch_argmax_reduce(am.val, am.idx, am.sum, am.ld, (int)slices, M, argmax_out, lse_out, nullptr, 0, round_dtype, N, stream);
 }
 
 }  // namespace b200
