@@ -26,8 +26,9 @@
 // product, 2 = argmax and log-sum-exp, 3 = argmax, optional log-sum-exp and the value at a per-row target column
 // with nothing stored.  On a power-capped part every epilogue instruction per output element shows up in the
 // clock of the main loop, so the epilogue is kept lean: packed fp32x2 adds/multiplies, no add without a bias,
-// the row maximum by packed 16-bit max instructions over the rounded values with one column look-up per tile
-// in the staging boxes, per-slice partials reduced by a small second kernel.
+// the row maximum by packed 16-bit max instructions over the rounded values; which column it sits in is looked up
+// once per tile in the staging boxes when nothing is stored, and left to the small second kernel that reduces the
+// per-slice partials when the product is stored (it re-reads the 32 stored values of the one chunk that wins the row).
 #include <string.h>
 
 #include <atomic>
