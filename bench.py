@@ -482,6 +482,10 @@ def run_gpu_arm(args, rank, world, local_rank):
             "roofline": {"kernel": "gemm_tn_kernel (tcgen05, all GEMM shapes of the forward)", "bound": "tensor",
                          "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved_tflops / peak_tflops,
                          "peak_source": f"{peak_kind}: cuBLAS bf16 sustained",
+                         "note": "the times of the LayerNorm-aware GEMMs include their share of the folded LayerNorms (statistics in the epilogue, "
+                                 "merge kernel, extension k-block); measured in eager passes after the timed loops",
+                         # the whole replayed step (every kernel, tensor-core flop only) against the same peak
+                         "whole_step": {"achieved": per_gpu_flops_s / 1e12, "frac": per_gpu_flops_s / (peak_tflops * 1e12)},
                          # DRAM bytes of one full-size c_fc launch (153600 x 3072 x 768) as ncu counted them
                          "traffic": traffic, "traffic_source": traffic_source,
                          "traffic_algorithmic": 2.0 * (153600 * 768 + 768 * 3072 + 153600 * 3072),

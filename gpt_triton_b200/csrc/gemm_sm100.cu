@@ -1132,23 +1132,39 @@ ln_stats_from_moments_kernel(const float2* __restrict__ moments, int64_t ld, int
   const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
-  if (row >= M) return;
+  const bool active = row < M;  // (no early return: the whole warp takes part in the shuffles below)
+  const int64_t rrow = active ? row : M - 1;
   float wsum = 0.f;
-  for (int s = 0; s < slices; ++s) wsum = fmaf((float)min(slice_cols, cols - s * slice_cols), moments[(int64_t)s * ld + row].x, wsum);
+  for (int s = 0; s < slices; ++s) wsum = fmaf((float)min(slice_cols, cols - s * slice_cols), moments[(int64_t)s * ld + rrow].x, wsum);
   const float mean = wsum / (float)cols;
   float m2 = 0.f;
   for (int s = 0; s < slices; ++s) {
-    const float2 part = moments[(int64_t)s * ld + row];
+    const float2 part = moments[(int64_t)s * ld + rrow];
     const float d = part.x - mean;
     m2 += fmaf((float)min(slice_cols, cols - s * slice_cols) * d, d, part.y);
   }
   const float sd = sqrtf(m2 / (float)cols + eps);
-  stats[row] = make_float2(mean, 1.0f / sd);
+  if (active) stats[row] = make_float2(mean, 1.0f / sd);
   if (ext) {
-    uint4* dst = reinterpret_cast<uint4*>(ext + row * kLnExtCols);
-    dst[0] = ln_ext_head<T>(mean, sd);
+    // The extensions of a warp's 32 consecutive rows are 4 KB of consecutive memory (16 meaningful bytes and 112
+    // zero bytes per row): written as 8 fully coalesced 512-byte warp stores, the heads fetched by shuffle.
+    const uint4 head = ln_ext_head<T>(mean, sd);
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_row0 = row - lane;
+    uint4* dst = reinterpret_cast<uint4*>(ext + warp_row0 * kLnExtCols);
+    constexpr int kChunksPerRow = kLnExtCols * 2 / 16;  // 8
 #pragma unroll
-    for (int i = 1; i < kLnExtCols * 2 / 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = 0; i < kChunksPerRow; ++i) {
+      const int chunk = i * 32 + lane;          // 16-byte chunk of the warp's 4 KB
+      const int src = chunk / kChunksPerRow;    // the row (lane) it belongs to
+      uint4 v;
+      v.x = __shfl_sync(0xffffffffu, head.x, src);
+      v.y = __shfl_sync(0xffffffffu, head.y, src);
+      v.z = __shfl_sync(0xffffffffu, head.z, src);
+      v.w = __shfl_sync(0xffffffffu, head.w, src);
+      if (chunk % kChunksPerRow != 0) v = make_uint4(0u, 0u, 0u, 0u);
+      if (warp_row0 + src < M) dst[chunk] = v;
+    }
   }
 }
 
