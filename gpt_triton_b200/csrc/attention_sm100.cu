@@ -3,8 +3,8 @@
 // reference, and both operands of one MMA must have the same format, so a bf16 V tile is converted to
 // fp16 in place (exact in fp16's normal range) by the softmax warps before P V.
 //
-// Work item = 128 query rows of one (batch, head).  Persistent CTAs (two per SM) walk the items,
-// longest first.  Per CTA:
+// Work item = up to 128 query rows of one (batch, head); a ragged sequence length puts its short tile first
+// (see decode_item).  Persistent CTAs (two per SM) walk the items, longest first.  Per CTA:
 //   warp 0      TMA producer: the 128x64 Q tile (double-buffered) and, per 64-key block, the K and V tiles
 //               (3-stage ring), all 128-byte swizzled, straight out of the strided q/k/v views (4-D tensor
 //               maps: head_dim, row, head, batch); every CTA issues its own loads
@@ -80,18 +80,28 @@ __host__ __device__ constexpr uint32_t idesc(int a_fmt, int b_fmt, int b_mn_majo
 }
 
 struct Item {
-  int b, h, q0, nblk;
+  int b, h, q0, q_end, nblk;
 };
+// Query rows [0, L) are cut into n_qt = ceil(L / 128) tiles of at most 128 rows whose ENDS are as early as they can be:
+// tile i ends at min(L, round_up(L - 128 * (n_qt - 1 - i), 64)) and starts where tile i - 1 ends.  A tile costs one
+// 64-key block per 64 rows up to its end, so a ragged L puts its short tile first, where the causal rows are
+// shortest (L = 300: rows [0,64) [64,192) [192,300) = 1 + 3 + 5 key blocks, where [0,128) [128,256) [256,300) would
+// take 2 + 4 + 5); starts stay multiples of 64, so only the last two key blocks of a tile need per-element masks.
+// A tile always loads 128 rows of Q; rows at or beyond its end are computed and dropped.
 // Items ordered by decreasing row-tile index (the longest causal rows first), then (batch, head).
+__device__ __forceinline__ int tile_end(int i, int n_qt, int L) {
+  const int e = (L - BLOCK_M * (n_qt - 1 - i) + BLOCK_N - 1) / BLOCK_N * BLOCK_N;
+  return min(L, e);
+}
 __device__ __forceinline__ Item decode_item(int64_t idx, int bh_total, int n_qt, int NH, int L) {
   const int qt = n_qt - 1 - (int)(idx / bh_total);
   const int bh = (int)(idx % bh_total);
   Item it;
   it.b = bh / NH;
   it.h = bh % NH;
-  it.q0 = qt * BLOCK_M;
-  const int last_row = min(it.q0 + BLOCK_M, L) - 1;
-  it.nblk = last_row / BLOCK_N + 1;
+  it.q0 = qt == 0 ? 0 : tile_end(qt - 1, n_qt, L);
+  it.q_end = tile_end(qt, n_qt, L);
+  it.nblk = (it.q_end - 1) / BLOCK_N + 1;
   return it;
 }
 
@@ -320,7 +330,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const Item it = decode_item(idx, bh_total, n_qt, p.NH, p.L);
       const int row = it.q0 + r_in_tile;
       const int warp_row0 = it.q0 + quarter * 32;       // first query row of this warp
-      const bool warp_live = warp_row0 < p.L;           // a warp whose 32 rows all lie beyond L only keeps the handshakes going
+      const bool warp_live = warp_row0 < it.q_end;      // a warp whose 32 rows all lie beyond the tile's end only keeps the handshakes going
       float m_run = -INFINITY, l_run = 0.f;             // l_run: this thread's half of the row's denominator
       for (int j = 0; j < it.nblk; ++j, ++it_count) {
         const uint32_t sb = it_count & 1;
@@ -455,7 +465,7 @@ attention_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) w[i] = pack_out<T>(__uint_as_float(a[2 * i]) * inv, __uint_as_float(a[2 * i + 1]) * inv);
-        if (row < p.L) {
+        if (row < it.q_end) {
           if (p.out_vec32) {
             st_global_v8(dst, &w[0]);
             st_global_v8(dst + 16, &w[8]);
