@@ -40,6 +40,12 @@ SIGNATURES = {
     "b200_ffn": (c_int, [c_void_p] * 5 + [c_i64] * 4 + [c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "b200_ffn_static_scratch": (c_int, [c_void_p] * 5 + [c_i64] * 4 + [c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200_attention": (c_int, [c_void_p] * 4 + [c_i64] * 4 + [_p_i64] * 4 + [c_float, c_int, c_int, c_void_p, c_void_p]),
+    "b200_embedding_at": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_void_p, c_float, c_void_p, c_void_p,
+                                  c_void_p, c_void_p]),
+    "b200_kv_cache_fill": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_int, c_void_p]),
+    "b200_attention_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_i64, c_i64, c_float, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_decode_append": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_sample_logits": (c_int, [c_void_p, c_i64, c_i64, c_i64, c_int, c_float, c_int, ctypes.c_uint64, c_void_p, c_void_p, c_void_p]),
     "b200_selftest_bounded_wait": (c_int, [c_void_p, c_i64, c_void_p]),
 }
 

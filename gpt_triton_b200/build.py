@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libb200gpt.so")
-SOURCES = ["api.cu", "elementwise.cu", "gemm_sm100.cu", "attention.cu", "attention_sm100.cu", "ffn_static_scratch.cu", "selftest.cu"]
+SOURCES = ["api.cu", "elementwise.cu", "gemm_sm100.cu", "attention.cu", "attention_sm100.cu", "decode.cu", "ffn_static_scratch.cu", "selftest.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "sm100_primitives.cuh"),
            os.path.join(os.path.dirname(PKG_DIR), "include", "b200_gpt.h")]
 NVCC_FLAGS = [

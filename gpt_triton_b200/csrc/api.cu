@@ -36,7 +36,7 @@ const char* b200_status_string(int status) {
 
 const char* b200_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
 
-int b200_abi_version(void) { return 5; }
+int b200_abi_version(void) { return 6; }
 
 uint64_t b200_launch_count(void) { return b200::launches_so_far(); }
 
@@ -46,7 +46,7 @@ int b200_embedding(const int64_t* ids, const void* wte, const void* wpe, void* o
   if (L > P) return B200_ERR_BAD_ARGUMENT;
   if (B * L == 0 || H == 0) return B200_OK;
   if (!ids || !wte || !wpe || !out) return B200_ERR_BAD_ARGUMENT;
-  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, nullptr, nullptr, 0.f, (cudaStream_t)stream));
+  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, nullptr, nullptr, 0.f, nullptr, (cudaStream_t)stream));
 }
 
 int b200_embedding_ln_stats(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t B, int64_t L, int64_t V,
@@ -56,7 +56,50 @@ int b200_embedding_ln_stats(const int64_t* ids, const void* wte, const void* wpe
   if (B * L == 0 || H == 0) return B200_OK;
   if (!ids || !wte || !wpe || !out || !ln_stats_out || (reinterpret_cast<uintptr_t>(ln_stats_out) & 7) || (reinterpret_cast<uintptr_t>(ln_ext_out) & 15))
     return B200_ERR_BAD_ARGUMENT;
-  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, ln_stats_out, ln_ext_out, eps, (cudaStream_t)stream));
+  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, ln_stats_out, ln_ext_out, eps, nullptr, (cudaStream_t)stream));
+}
+
+// ------------------------------------------------------------------ token-by-token generation
+int b200_embedding_at(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t B, int64_t L, int64_t V, int64_t P, int64_t H,
+                      int dtype, int* bad_id_flag, float eps, float* ln_stats_out, void* ln_ext_out, const int32_t* pos0_dev, void* stream) {
+  if (B < 0 || L < 0 || V < 1 || P < 1 || H < 0 || !valid_dtype(dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (L > P) return B200_ERR_BAD_ARGUMENT;
+  if (B * L == 0 || H == 0) return B200_OK;
+  if (!ids || !wte || !wpe || !out || !pos0_dev || (reinterpret_cast<uintptr_t>(pos0_dev) & 3) || (ln_ext_out && !ln_stats_out) ||
+      (reinterpret_cast<uintptr_t>(ln_stats_out) & 7) || (reinterpret_cast<uintptr_t>(ln_ext_out) & 15))
+    return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_embedding(ids, wte, wpe, out, B * L, L, V, P, H, dtype, bad_id_flag, ln_stats_out, ln_ext_out, eps, pos0_dev, (cudaStream_t)stream));
+}
+
+int b200_kv_cache_fill(const void* qkv, void* cache, int64_t B, int64_t L, int64_t H, int64_t cache_len, int dtype, void* stream) {
+  if (B < 0 || L < 0 || H < 0 || cache_len < L || !valid_dtype(dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (B == 0 || L == 0 || H == 0) return B200_OK;
+  if (!qkv || !cache) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_kv_cache_fill(qkv, cache, B, L, H, cache_len, dtype, (cudaStream_t)stream));
+}
+
+int b200_attention_decode(const void* qkv_new, void* cache, void* out, int64_t B, int64_t NH, int64_t D, int64_t cache_len, float scale, int dtype,
+                          const int32_t* pos_dev, int* status_word, void* stream) {
+  if (B < 0 || NH < 0 || D < 1 || cache_len < 1 || !valid_dtype(dtype)) return B200_ERR_BAD_ARGUMENT;
+  if (D != 32 && D != 64 && D != 128) return B200_ERR_UNSUPPORTED;
+  if (B == 0 || NH == 0) return B200_OK;
+  if (!qkv_new || !cache || !out || !pos_dev || (reinterpret_cast<uintptr_t>(pos_dev) & 3)) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_attention_decode(qkv_new, cache, out, B, NH, D, cache_len, scale, dtype, pos_dev, status_word, (cudaStream_t)stream));
+}
+
+int b200_decode_append(const int64_t* next_ids, int64_t* tokens, int64_t ld_tokens, int64_t n_cols, int64_t B, int32_t* pos_dev, int advance,
+                       int64_t* feedback, int* status_word, void* stream) {
+  if (B < 0 || n_cols < 1 || ld_tokens < n_cols) return B200_ERR_BAD_ARGUMENT;
+  if (!next_ids || !tokens || !pos_dev || (reinterpret_cast<uintptr_t>(pos_dev) & 3)) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_decode_append(next_ids, tokens, ld_tokens, n_cols, B, pos_dev, advance, feedback, status_word, (cudaStream_t)stream));
+}
+
+int b200_sample_logits(const void* logits, int64_t ld, int64_t B, int64_t V, int dtype, float temperature, int top_k, uint64_t seed,
+                       const int32_t* step_dev, int64_t* ids_out, void* stream) {
+  if (B < 0 || V < 1 || ld < V || !valid_dtype(dtype) || !(temperature > 0.f) || top_k < 0) return B200_ERR_BAD_ARGUMENT;
+  if (B == 0) return B200_OK;
+  if (!logits || !ids_out || (reinterpret_cast<uintptr_t>(step_dev) & 3)) return B200_ERR_BAD_ARGUMENT;
+  return note(b200::launch_sample_rows(logits, ld, B, V, dtype, temperature, top_k, seed, step_dev, ids_out, (cudaStream_t)stream));
 }
 
 int b200_row_ln_stats(const void* x, float* ln_stats_out, void* ln_ext_out, int64_t M, int64_t H, float eps, int dtype, void* stream) {

@@ -209,8 +209,18 @@ uint64_t launches_so_far();
 // ------------------------------------------------------------------ internal launchers
 // ln_stats (optional, fp32 pairs [T]): (mean, 1 / sqrt(variance + eps)) of every stored row; ln_ext (with it): the
 // rows' extensions [T, kLnExtCols] in the storage type (16-bit types only)
+// pos0_dev (optional, device int32): position of each sequence's first token (token-by-token generation); NULL = 0
 int launch_embedding(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t T, int64_t L, int64_t V,
-                     int64_t P, int64_t H, int dtype, int* bad_id_flag, float* ln_stats, void* ln_ext, float eps, cudaStream_t stream);
+                     int64_t P, int64_t H, int dtype, int* bad_id_flag, float* ln_stats, void* ln_ext, float eps, const int* pos0_dev,
+                     cudaStream_t stream);
+// Token-by-token generation (decode.cu).  pos_dev: device int32 pair {tokens in the cache, prompt length}.
+int launch_kv_cache_fill(const void* qkv, void* cache, int64_t B, int64_t L, int64_t H, int64_t cache_len, int dtype, cudaStream_t stream);
+int launch_attention_decode(const void* qkv_new, void* cache, void* out, int64_t B, int64_t NH, int64_t D, int64_t cache_len, float scale, int dtype,
+                            const int* pos_dev, int* status_word, cudaStream_t stream);
+int launch_decode_append(const int64_t* next_ids, int64_t* tokens, int64_t ld_tokens, int64_t n_cols, int64_t B, int* pos_dev, int advance,
+                         int64_t* feedback, int* status_word, cudaStream_t stream);
+int launch_sample_rows(const void* logits, int64_t ld, int64_t B, int64_t V, int dtype, float temperature, int top_k, uint64_t seed,
+                       const int* step_dev, int64_t* ids_out, cudaStream_t stream);
 int launch_row_ln_stats(const void* x, float* ln_stats, void* ln_ext, int64_t M, int64_t H, float eps, int dtype, cudaStream_t stream);
 int launch_fold_layernorm(const void* w, const void* gamma, const void* beta, const void* bias, void* packed, float* colsum, float* bias_out,
                           void* w_ext, int64_t K, int64_t N, int64_t ld_dst, int dtype, cudaStream_t stream);

@@ -51,18 +51,21 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 embedding_kernel(const int64_t* __restrict__ ids, const T* __restrict__ wte, const T* __restrict__ wpe,
                  T* __restrict__ out, int64_t T_rows, int64_t L, int64_t V, int64_t H, int* bad_id_flag, float2* __restrict__ stats, T* __restrict__ ext,
-                 float eps) {
+                 float eps, const int* __restrict__ pos0_dev, int64_t P) {
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int64_t stride = (int64_t)gridDim.x * kWarpsPerBlock;
   pdl_launch_dependents();
   pdl_wait();
+  // position of a sequence's first token: 0, or (token-by-token generation) read from device memory
+  const int64_t pos0 = pos0_dev ? pos0_dev[0] : 0;
   for (int64_t t = warp0; t < T_rows; t += stride) {
     const int64_t id = ids[t];
-    const bool ok = id >= 0 && id < V;
+    const int64_t pos = pos0 + t % L;
+    const bool ok = id >= 0 && id < V && pos >= 0 && pos < P;  // (pos < P always holds when pos0 is 0: the host checked L <= P)
     if (!ok && lane == 0 && bad_id_flag) *bad_id_flag = 1;
     const T* e = wte + (ok ? id : 0) * H;
-    const T* p = wpe + (t % L) * H;
+    const T* p = wpe + (ok ? pos : 0) * H;
     T* o = out + t * H;
     // sums of (value - shift) and its square over the values as stored; the shift (the row's first value) keeps the
     // centred sum of squares free of cancellation
@@ -157,25 +160,25 @@ static unsigned row_grid(int64_t rows) {
 
 template <typename T>
 static int embedding_typed(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t T_rows, int64_t L,
-                           int64_t V, int64_t H, int* flag, float2* stats, void* ext, float eps, cudaStream_t stream) {
+                           int64_t V, int64_t H, int* flag, float2* stats, void* ext, float eps, const int* pos0_dev, int64_t P, cudaStream_t stream) {
   const bool vec = (H % 8 == 0) && ((reinterpret_cast<uintptr_t>(wte) | reinterpret_cast<uintptr_t>(wpe) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   LaunchSetup ls(dim3(row_grid(T_rows)), dim3(kWarpsPerBlock * 32), 0, stream);
-  const cudaError_t e = vec ? cudaLaunchKernelEx(&ls.cfg, embedding_kernel<T, true>, ids, (const T*)wte, (const T*)wpe, (T*)out, T_rows, L, V, H, flag, stats, (T*)ext, eps)
-                            : cudaLaunchKernelEx(&ls.cfg, embedding_kernel<T, false>, ids, (const T*)wte, (const T*)wpe, (T*)out, T_rows, L, V, H, flag, stats, (T*)ext, eps);
+  const cudaError_t e = vec ? cudaLaunchKernelEx(&ls.cfg, embedding_kernel<T, true>, ids, (const T*)wte, (const T*)wpe, (T*)out, T_rows, L, V, H, flag, stats, (T*)ext, eps, pos0_dev, P)
+                            : cudaLaunchKernelEx(&ls.cfg, embedding_kernel<T, false>, ids, (const T*)wte, (const T*)wpe, (T*)out, T_rows, L, V, H, flag, stats, (T*)ext, eps, pos0_dev, P);
   note_launches(1);
   return status_from_cuda(e);
 }
 
 int launch_embedding(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t T_rows, int64_t L,
-                     int64_t V, int64_t P, int64_t H, int dtype, int* bad_id_flag, float* ln_stats, void* ln_ext, float eps, cudaStream_t stream) {
-  (void)P;
+                     int64_t V, int64_t P, int64_t H, int dtype, int* bad_id_flag, float* ln_stats, void* ln_ext, float eps, const int* pos0_dev,
+                     cudaStream_t stream) {
   if (T_rows == 0 || H == 0) return B200_OK;
   if (ln_ext && (dtype == B200_F32 || !ln_stats)) return B200_ERR_UNSUPPORTED;
   float2* st = reinterpret_cast<float2*>(ln_stats);
   switch (dtype) {
-    case B200_F32: return embedding_typed<float>(ids, wte, wpe, out, T_rows, L, V, H, bad_id_flag, st, nullptr, eps, stream);
-    case B200_F16: return embedding_typed<__half>(ids, wte, wpe, out, T_rows, L, V, H, bad_id_flag, st, ln_ext, eps, stream);
-    case B200_BF16: return embedding_typed<__nv_bfloat16>(ids, wte, wpe, out, T_rows, L, V, H, bad_id_flag, st, ln_ext, eps, stream);
+    case B200_F32: return embedding_typed<float>(ids, wte, wpe, out, T_rows, L, V, H, bad_id_flag, st, nullptr, eps, pos0_dev, P, stream);
+    case B200_F16: return embedding_typed<__half>(ids, wte, wpe, out, T_rows, L, V, H, bad_id_flag, st, ln_ext, eps, pos0_dev, P, stream);
+    case B200_BF16: return embedding_typed<__nv_bfloat16>(ids, wte, wpe, out, T_rows, L, V, H, bad_id_flag, st, ln_ext, eps, pos0_dev, P, stream);
   }
   return B200_ERR_BAD_ARGUMENT;
 }

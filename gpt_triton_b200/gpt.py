@@ -117,22 +117,46 @@ class FusedAttention(_EvalOnly):
         self.c_proj_bias = _uniform(hidden_size)
         self._operand = _OperandCache()
 
-    def forward(self, x):
+    def forward(self, x, kv_cache=None):
+        """``kv_cache`` (batch, capacity, 2 * hidden), optional: receives the keys and values of these positions
+        (the prompt of a generation)."""
         self._check_eval()
         skip = x
         y = K.fused_layer_norm(x, self.layer_norm_weight.data, self.layer_norm_bias.data)
-        q, k, v = K.matmul_and_split_qkv(y, self._operand(self.c_attn_weight), self.c_attn_bias.data, self.num_heads)
+        qkv = K.fused_ffn(y, self._operand(self.c_attn_weight), bias=self.c_attn_bias.data)
+        if kv_cache is not None:
+            K.kv_cache_fill(qkv, kv_cache)
+        q, k, v = K.split_qkv(qkv, self.num_heads)
         y = K.flash_attention_v1(q, k, v, merged_heads=True).view(skip.shape)
         return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=skip)
 
-    def forward_folded(self, x, stats, return_row_stats=True):
+    def forward_folded(self, x, stats, return_row_stats=True, kv_cache=None):
         """The same block with its LayerNorm folded into c_attn: x (batch, seqlen, hidden) are the raw rows,
         `stats` their RowStats.  Returns (output, RowStats of the output) for the block that follows."""
         self._check_eval()
         w = self._operand.folded(self.c_attn_weight, self.layer_norm_weight, self.layer_norm_bias, self.c_attn_bias)
-        q, k, v = K.split_qkv(K.fused_ffn(x, w, ln_stats=stats), self.num_heads)
+        qkv = K.fused_ffn(x, w, ln_stats=stats)
+        if kv_cache is not None:
+            K.kv_cache_fill(qkv, kv_cache)
+        q, k, v = K.split_qkv(qkv, self.num_heads)
         y = K.flash_attention_v1(q, k, v, merged_heads=True).view(x.shape)
         if not return_row_stats:
+            return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=x), None
+        return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=x, return_row_stats=True)
+
+    def decode(self, x, stats, kv_cache, pos):
+        """One generated token per sequence: x (batch, hidden) are the raw rows of the token at position pos[0],
+        `stats` their RowStats (None: unfolded LayerNorm, as in forward()).  Its keys and values join `kv_cache` and
+        its query attends over positions 0..pos[0].  Returns (output (batch, hidden), RowStats or None)."""
+        self._check_eval()
+        if stats is not None:
+            w = self._operand.folded(self.c_attn_weight, self.layer_norm_weight, self.layer_norm_bias, self.c_attn_bias)
+            qkv = K.fused_ffn(x, w, ln_stats=stats)
+        else:
+            y = K.fused_layer_norm(x, self.layer_norm_weight.data, self.layer_norm_bias.data)
+            qkv = K.fused_ffn(y, self._operand(self.c_attn_weight), bias=self.c_attn_bias.data)
+        y = K.attention_decode(qkv, kv_cache, pos, self.num_heads)
+        if stats is None:
             return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=x), None
         return K.fused_ffn(y, self._operand(self.c_proj_weight), bias=self.c_proj_bias.data, residual=x, return_row_stats=True)
 
@@ -202,20 +226,82 @@ class FusedGPT(_EvalOnly):
         _ln_params(self, h)
         self._operand = _OperandCache()
 
-    def forward(self, x):
-        """ids (batch, seqlen) -> final hidden state (batch, seqlen, n_embd)."""
+    def _folds(self):
+        return self.fold_layer_norm and self.wte_weight.dtype in (torch.float16, torch.bfloat16) and self.config.n_embd % 8 == 0
+
+    def _body(self, x, kv_caches=None):
+        """ids (batch, seqlen) -> residual stream before the final LayerNorm; kv_caches: one tensor per layer that
+        receives the layer's keys and values (the prompt of a generation)."""
         self._check_eval()
-        if self.fold_layer_norm and self.wte_weight.dtype in (torch.float16, torch.bfloat16) and self.config.n_embd % 8 == 0:
+        cache = (lambda i: None) if kv_caches is None else (lambda i: kv_caches[i])
+        if self._folds():
             y, stats = K.fused_embeddings(x, self.wte_weight.data, self.wpe_weight.data, return_row_stats=True)
             last = len(self.blocks) - 1
             for i, (attention, mlp) in enumerate(self.blocks):
-                y, stats = attention.forward_folded(y, stats)
+                y, stats = attention.forward_folded(y, stats, kv_cache=cache(i))
                 y, stats = mlp.forward_folded(y, stats, return_row_stats=i != last)  # the final LayerNorm stays a kernel
         else:
             y = K.fused_embeddings(x, self.wte_weight.data, self.wpe_weight.data)
-            for attention, mlp in self.blocks:
-                y = mlp(attention(y))
+            for i, (attention, mlp) in enumerate(self.blocks):
+                y = mlp(attention(y, kv_cache=cache(i)))
+        return y
+
+    def forward(self, x):
+        """ids (batch, seqlen) -> final hidden state (batch, seqlen, n_embd)."""
+        return K.fused_layer_norm(self._body(x), self.layer_norm_weight.data, self.layer_norm_bias.data)
+
+    def _decode_body(self, ids, kv_caches, pos):
+        """ids (batch,) of the tokens at position pos[0] -> their final hidden state (batch, n_embd); their keys and
+        values join the caches."""
+        self._check_eval()
+        B = ids.shape[0]
+        if self._folds():
+            y, stats = K.fused_embeddings(ids.view(B, 1), self.wte_weight.data, self.wpe_weight.data, return_row_stats=True, position=pos)
+            y = y.view(B, -1)
+            last = len(self.blocks) - 1
+            for i, (attention, mlp) in enumerate(self.blocks):
+                y, stats = attention.decode(y, stats, kv_caches[i], pos)
+                y, stats = mlp.forward_folded(y, stats, return_row_stats=i != last)
+        else:
+            y = K.fused_embeddings(ids.view(B, 1), self.wte_weight.data, self.wpe_weight.data, position=pos).view(B, -1)
+            for i, (attention, mlp) in enumerate(self.blocks):
+                y = mlp(attention.decode(y, None, kv_caches[i], pos)[0])
         return K.fused_layer_norm(y, self.layer_norm_weight.data, self.layer_norm_bias.data)
+
+    def _pick(self, hidden, temperature, top_k, seed, pos):
+        """hidden (batch, n_embd), final LayerNorm applied -> next ids (batch,) int64: greedy (temperature 0: row
+        argmax in the lm_head's epilogue, logits not written for 16-bit models) or sampled."""
+        B, h = hidden.shape
+        w = self._operand(self.wte_weight, weight_is_nk=True)
+        if temperature == 0.0 and hidden.dtype != torch.float32:
+            return K.ffn_row_statistics(hidden, w, want_lse=False)[0]
+        V = self.config.vocab_size
+        pitch = (V + 63) // 64 * 64
+        buf = torch.empty((B, pitch), device=hidden.device, dtype=hidden.dtype)
+        logits = K.fused_ffn(hidden, w, out=buf[:, :V])
+        if temperature == 0.0:
+            return logits.argmax(dim=-1)
+        return K.sample_logits(logits, temperature=temperature, top_k=top_k, seed=seed, step=pos)
+
+    @torch.no_grad()
+    def generate(self, ids, max_new_tokens, temperature=0.0, top_k=0, seed=0, use_cuda_graph=True):
+        """ids (batch, prompt_len) -> (batch, max_new_tokens) int64 continuation, one token per step with a key/value
+        cache (the inference loop the reference's README.md:55 lists as not built).  temperature 0: greedy; > 0:
+        draws from softmax(logits / temperature) over the top_k largest logits (0 = all), reproducible for a given
+        seed.  The sessions (cache, captured decode step) are kept on the model per
+        (batch, capacity, temperature, top_k, seed) and re-used by later calls of the same shape."""
+        B, L0 = ids.shape
+        need = L0 + max_new_tokens - 1
+        key = (B, temperature, top_k, seed, use_cuda_graph, self.wte_weight.dtype, self.wte_weight.device)
+        sessions = self.__dict__.setdefault("_sessions", {})
+        session = sessions.get(key)
+        if session is None or session.capacity < need or session.tokens.shape[1] < max_new_tokens or session.stale():
+            sessions.pop(key, None)
+            while len(sessions) >= 4:  # every session holds a cache: keep a few
+                sessions.pop(next(iter(sessions)))
+            sessions[key] = session = GenerationSession(self, B, capacity=need, max_new_tokens=max_new_tokens, temperature=temperature,
+                                                        top_k=top_k, seed=seed, use_cuda_graph=use_cuda_graph)
+        return session.generate(ids, max_new_tokens)
 
     @torch.no_grad()
     def lm_head(self, hidden, return_argmax=False, return_lse=False):
@@ -327,6 +413,78 @@ class GraphedForward:
         self.static_ids.copy_(ids)
         self.graph.replay()
         return self.outputs
+
+
+class GenerationSession:
+    """Token-by-token generation for a fixed batch size: the key/value cache of every layer
+    ((batch, capacity, 2 * n_embd) each), the device-side position counter and, after the first two decode steps,
+    a CUDA graph of one decode step that is replayed for every further token of this and later generations (any
+    prompt length: the position lives in device memory).  Prompt + generated tokens - 1 must fit both `capacity`
+    and the model's position table.  No counterpart in the reference (README.md:55)."""
+
+    EAGER_STEPS = 2  # decode steps run eagerly before the capture (kernel attributes, allocator pools)
+
+    def __init__(self, model, batch, capacity, max_new_tokens, temperature=0.0, top_k=0, seed=0, use_cuda_graph=True):
+        cfg = model.config
+        assert capacity <= cfg.block_size, f"{capacity} positions exceed the position table ({cfg.block_size} rows)"
+        assert temperature >= 0.0 and top_k >= 0 and max_new_tokens >= 1
+        dev, dtype = model.wte_weight.device, model.wte_weight.dtype
+        self.model, self.batch, self.capacity = model, batch, max(int(capacity), 1)
+        self.temperature, self.top_k, self.seed, self.use_cuda_graph = float(temperature), int(top_k), int(seed), use_cuda_graph
+        self.kv = [torch.empty((batch, self.capacity, 2 * cfg.n_embd), device=dev, dtype=dtype) for _ in range(cfg.n_layer)]
+        self.pos = torch.zeros(2, device=dev, dtype=torch.int32)  # {tokens in the cache, prompt length}
+        self.tokens = torch.zeros((batch, max_new_tokens), device=dev, dtype=torch.int64)
+        self.feedback = torch.zeros((batch,), device=dev, dtype=torch.int64)  # the ids the next decode step embeds
+        self.graph = None
+        self._sig = self._signature()
+
+    def _signature(self):
+        return tuple(_OperandCache._tag(p) for p in self.model.parameters())
+
+    def stale(self):
+        """True once a parameter has been reloaded, cast or moved: a captured step holds the old operands."""
+        return self._signature() != self._sig
+
+    def _step(self):
+        m = self.model
+        hidden = m._decode_body(self.feedback, self.kv, self.pos)
+        ids = m._pick(hidden, self.temperature, self.top_k, self.seed, self.pos)
+        K.decode_append(ids, self.tokens, self.pos, advance=True, feedback=self.feedback)
+
+    @torch.no_grad()
+    def generate(self, ids, max_new_tokens):
+        m = self.model
+        B, L0 = ids.shape
+        assert B == self.batch and L0 >= 1 and 1 <= max_new_tokens <= self.tokens.shape[1]
+        assert L0 + max_new_tokens - 1 <= self.capacity, "prompt + generated tokens do not fit this session's cache"
+        assert not self.stale(), "the model's parameters changed: make a new session"
+        dev = self.pos.device
+        # prompt: the usual forward, its keys/values copied into the caches; next id from the last position
+        y = m._body(ids, kv_caches=self.kv)
+        last = K.fused_layer_norm(y[:, -1, :].contiguous(), m.layer_norm_weight.data, m.layer_norm_bias.data)
+        self.pos.copy_(torch.tensor([L0, L0], dtype=torch.int32), non_blocking=False)
+        first = m._pick(last, self.temperature, self.top_k, self.seed, self.pos)
+        K.decode_append(first, self.tokens, self.pos, advance=False, feedback=self.feedback)
+        steps = max_new_tokens - 1
+        done = 0
+        if self.graph is None:
+            while done < min(steps, self.EAGER_STEPS):
+                self._step()
+                done += 1
+            if self.use_cuda_graph and done < steps:
+                torch.cuda.synchronize(dev)
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph):
+                    self._step()
+        for _ in range(steps - done):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._step()
+        code = K.device_status(dev)
+        if code:
+            raise RuntimeError(f"generation stopped by a device-side check (code {code}): cache or token buffer out of room")
+        return self.tokens[:, :max_new_tokens].clone()
 
 
 def executed_fwd_flops(config, batch, seqlen, with_lm_head=True):

@@ -133,9 +133,11 @@ def row_stats(x):
 
 
 @torch.no_grad()
-def fused_embeddings(x, wte, wpe, dropout_prob=0.0, *, return_row_stats=False):
+def fused_embeddings(x, wte, wpe, dropout_prob=0.0, *, return_row_stats=False, position=None):
     """z[b, l, :] = wte[x[b, l], :] + wpe[l, :]  (reference kernels.py:76-101).  With ``return_row_stats`` the
-    result is ``(z, RowStats of z's rows)``, taken while the rows are written."""
+    result is ``(z, RowStats of z's rows)``, taken while the rows are written.  ``position`` (a CUDA int32 tensor;
+    token-by-token generation) makes the first position ``position[0]``, read on the device at run time, instead
+    of 0."""
     _no_dropout(dropout_prob)
     require_cuda(x, wte, wpe)
     assert wte.shape[1] == wpe.shape[1]
@@ -151,6 +153,16 @@ def fused_embeddings(x, wte, wpe, dropout_prob=0.0, *, return_row_stats=False):
     if x.dtype != torch.int64:
         x = x.to(torch.int64)
     z = torch.empty((B * L, H), device=dev, dtype=wte.dtype)
+    if position is not None:
+        assert position.dtype == torch.int32 and position.device == dev and position.numel() >= 1
+        stats = torch.empty((max(B * L, 1), 2), device=dev, dtype=torch.float32) if return_row_stats else None
+        ext = torch.empty((max(B * L, 1), LN_EXT_COLS), device=dev, dtype=wte.dtype) if return_row_stats and wte.dtype != torch.float32 else None
+        with torch.cuda.device(dev):
+            st = _lib.load().b200_embedding_at(x.data_ptr(), wte.data_ptr(), wpe.data_ptr(), z.data_ptr(), B, L, V, P, H, dtype_code(wte.dtype),
+                                               None, LN_EPS, _ptr(stats), _ptr(ext), position.data_ptr(), stream_ptr(dev))
+        check(st, "fused_embeddings(position)")
+        z = z.view((B, L, H))
+        return (z, RowStats(stats[:B * L], H, None if ext is None else ext[:B * L])) if return_row_stats else z
     if return_row_stats:
         stats = torch.empty((max(B * L, 1), 2), device=dev, dtype=torch.float32)
         ext = torch.empty((max(B * L, 1), LN_EXT_COLS), device=dev, dtype=wte.dtype) if wte.dtype != torch.float32 else None
@@ -513,3 +525,82 @@ def flash_attention_v1(q, k, v, dropout_prob=0.0, *, merged_heads=False):
                                         dtype_code(z.dtype), _status_ptr(dev), stream_ptr(dev))
     check(st, "flash_attention_v1")
     return z.view(B, Lq, N * H) if merged_heads else z
+
+
+# ----------------------------------------------------------------------------- token-by-token generation
+# No counterpart in the reference (its README.md:55 lists "KV cache + sampling" as not built).  ``pos`` below is a
+# CUDA int32 tensor of two elements, {tokens in the cache, prompt length}: the kernels read it on the device, so the
+# launches of a decode step can be captured once in a CUDA graph and replayed for every step.
+@torch.no_grad()
+def kv_cache_fill(qkv, cache):
+    """cache[b, l, :] = qkv[b, l, H:3H] for the L positions of a prompt: qkv (B, L, 3H) is the fused c_attn output
+    (q | k | v), cache (B, cache_len, 2H) holds k | v.  Both contiguous, same dtype."""
+    require_cuda(qkv, cache)
+    B, L, H3 = qkv.shape
+    H = H3 // 3
+    assert H3 == 3 * H and cache.dim() == 3 and cache.shape[0] == B and cache.shape[2] == 2 * H and cache.shape[1] >= L
+    assert qkv.is_contiguous() and cache.is_contiguous() and qkv.dtype == cache.dtype
+    dev = _same_device(qkv, cache)
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_kv_cache_fill(qkv.data_ptr(), cache.data_ptr(), B, L, H, cache.shape[1], dtype_code(qkv.dtype), stream_ptr(dev))
+    check(st, "kv_cache_fill")
+    return cache
+
+
+@torch.no_grad()
+def attention_decode(qkv_new, cache, pos, num_heads):
+    """One decode step of causal attention: qkv_new (B, 3H) is q | k | v of the token at position pos[0]; its k, v are
+    stored into cache[:, pos[0]] and the result (B, H) is softmax(q K^T / sqrt(D)) V over positions 0..pos[0], with the
+    64-key online softmax of the reference's flash_attention_v1 (kernels.py:417-474)."""
+    require_cuda(qkv_new, cache, pos)
+    B, H3 = qkv_new.shape
+    H = H3 // 3
+    assert H3 == 3 * H and H % num_heads == 0
+    D = H // num_heads
+    assert D in (32, 64, 128), f"head size {D}: the decode kernel is built for 32, 64 and 128"
+    assert cache.dim() == 3 and cache.shape[0] == B and cache.shape[2] == 2 * H
+    assert qkv_new.is_contiguous() and cache.is_contiguous() and qkv_new.dtype == cache.dtype
+    assert pos.dtype == torch.int32 and pos.numel() >= 2
+    dev = _same_device(qkv_new, cache, pos)
+    out = torch.empty((B, H), device=dev, dtype=qkv_new.dtype)
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_attention_decode(qkv_new.data_ptr(), cache.data_ptr(), out.data_ptr(), B, num_heads, D, cache.shape[1],
+                                               1 / math.sqrt(D), dtype_code(qkv_new.dtype), pos.data_ptr(), _status_ptr(dev), stream_ptr(dev))
+    check(st, "attention_decode")
+    return out
+
+
+@torch.no_grad()
+def decode_append(next_ids, tokens, pos, advance, feedback=None):
+    """tokens[:, pos[0] - pos[1] + advance] = next_ids (and feedback[:] = next_ids, the buffer the next decode step
+    embeds), then pos[0] += 1 if advance -- all on the device."""
+    require_cuda(next_ids, tokens, pos, feedback)
+    if feedback is not None:
+        assert feedback.dtype == torch.int64 and feedback.is_contiguous() and feedback.numel() == next_ids.numel()
+    assert next_ids.dtype == tokens.dtype == torch.int64 and next_ids.is_contiguous() and tokens.dim() == 2 and tokens.stride(1) == 1
+    assert tokens.shape[0] == next_ids.numel() and pos.dtype == torch.int32 and pos.numel() >= 2
+    dev = _same_device(next_ids, tokens, pos, feedback)
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_decode_append(next_ids.data_ptr(), tokens.data_ptr(), tokens.stride(0) if tokens.shape[0] > 1 else tokens.shape[1],
+                                            tokens.shape[1], tokens.shape[0], pos.data_ptr(), int(bool(advance)), _ptr(feedback), _status_ptr(dev), stream_ptr(dev))
+    check(st, "decode_append")
+
+
+@torch.no_grad()
+def sample_logits(logits, temperature=1.0, top_k=0, seed=0, step=None, out=None):
+    """One id per row of logits (B, V), drawn from softmax(logits / temperature) over the row's top_k largest logits
+    (0 = all; ties with the k-th largest stay in).  Gumbel-max with counter-based uniforms: the same
+    (seed, step[0], row) always gives the same id.  ``step``: CUDA int32 tensor read on the device, or None for 0."""
+    require_cuda(logits, step)
+    assert logits.dim() == 2 and logits.stride(1) == 1 and temperature > 0 and top_k >= 0
+    B, V = logits.shape
+    dev = _same_device(logits, step)
+    ids = torch.empty((B,), device=dev, dtype=torch.int64) if out is None else out
+    assert ids.dtype == torch.int64 and ids.is_contiguous() and ids.numel() == B and ids.device == dev
+    if step is not None:
+        assert step.dtype == torch.int32 and step.numel() >= 1
+    with torch.cuda.device(dev):
+        st = _lib.load().b200_sample_logits(logits.data_ptr(), logits.stride(0) if B > 1 else V, B, V, dtype_code(logits.dtype), float(temperature),
+                                            int(top_k), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(step), ids.data_ptr(), stream_ptr(dev))
+    check(st, "sample_logits")
+    return ids

@@ -35,7 +35,7 @@ enum {
 const char* b200_status_string(int status);
 /* cudaGetErrorString of the last failing CUDA call made by this library on this thread. */
 const char* b200_last_cuda_error(void);
-/* ABI version of this header (5); bumped when a signature changes or an entry point is added. */
+/* ABI version of this header (6); bumped when a signature changes or an entry point is added. */
 int b200_abi_version(void);
 /* Number of kernels this library has launched in this process so far (all entry points). */
 uint64_t b200_launch_count(void);
@@ -237,6 +237,65 @@ int b200_ffn_static_scratch(const void* x, const void* w, const void* bias, cons
 int b200_attention(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t NH, int64_t L, int64_t D,
                    const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                    const int64_t o_strides[3], float scale, int in_dtype, int out_dtype, int* status_word, void* stream);
+
+/*
+ * Token-by-token generation: key/value cache, one-query attention, sampling.  None of these has a counterpart in
+ * the reference, which lists "KV cache + sampling" among the things it never built (README.md:55); the attention
+ * arithmetic follows its flash_attention_v1 (kernels.py:417-474), so that a cached step gives what re-running
+ * the whole sequence through b200_attention would, to rounding.
+ *
+ * Whatever changes from one generated token to the next is read from DEVICE memory, so the launches of a
+ * decode step can be recorded once in a CUDA graph and replayed: `pos_dev` is a device int32 pair, 4-byte aligned,
+ * pos_dev[0] = number of tokens whose keys/values are in the cache (= position of the token being decoded),
+ * pos_dev[1] = length of the prompt.  The cache of one layer is [B, cache_len, 2H] of the model's dtype, keys in
+ * columns [0, H), values in [H, 2H) (H = NH * D), 16-byte aligned.
+ */
+
+/*
+ * b200_embedding (with the optional LayerNorm outputs of b200_embedding_ln_stats: pass NULL for both, or
+ * ln_stats_out alone, or both) whose first position is *pos0_dev instead of 0:
+ * out[t,:] = wte[ids[t],:] + wpe[*pos0_dev + t % L,:].  A position outside [0, P) is treated like a bad id
+ * (zero row, *bad_id_flag = 1).
+ */
+int b200_embedding_at(const int64_t* ids, const void* wte, const void* wpe, void* out, int64_t B, int64_t L, int64_t V, int64_t P, int64_t H,
+                      int dtype, int* bad_id_flag, float eps, float* ln_stats_out, void* ln_ext_out, const int32_t* pos0_dev, void* stream);
+
+/*
+ * After the prompt's forward: cache[b, l, 0:2H] = qkv[b, l, H:3H] for l < L, from the fused c_attn output
+ * qkv [B, L, 3H] (q | k | v).  Needs L <= cache_len, H * element size a multiple of 16, 16-byte aligned pointers.
+ */
+int b200_kv_cache_fill(const void* qkv, void* cache, int64_t B, int64_t L, int64_t H, int64_t cache_len, int dtype, void* stream);
+
+/*
+ * One decode step of causal attention for every (batch, head): with pos = pos_dev[0], stores the new token's
+ * key and value (qkv_new [B, 3H] = q | k | v of that token) into cache[b, pos, :] and writes
+ * out[b, head*D : (head+1)*D] = softmax(q . K[0..pos]^T * scale) . V[0..pos]   (out [B, H]).
+ * D in {32, 64, 128}, else B200_ERR_UNSUPPORTED.  If pos is outside [0, cache_len) nothing is read or written and
+ * *status_word (device int*, may be NULL) receives the code 41.
+ */
+int b200_attention_decode(const void* qkv_new, void* cache, void* out, int64_t B, int64_t NH, int64_t D, int64_t cache_len, float scale, int dtype,
+                          const int32_t* pos_dev, int* status_word, void* stream);
+
+/*
+ * tokens[b, column] = next_ids[b] with column = pos_dev[0] - pos_dev[1] + (advance ? 1 : 0); then, if advance,
+ * pos_dev[0] += 1.  advance = 0 stores the token predicted by the prompt's forward (column 0), advance = 1 the
+ * one predicted by a decode step.  tokens [B, n_cols] int64 with row pitch ld_tokens; a column outside
+ * [0, n_cols) writes nothing and leaves the code 42 in *status_word.  feedback (int64 [B], may be NULL) receives
+ * the same ids: the fixed buffer the next decode step's b200_embedding_at reads, so a replayed step feeds itself.
+ */
+int b200_decode_append(const int64_t* next_ids, int64_t* tokens, int64_t ld_tokens, int64_t n_cols, int64_t B, int32_t* pos_dev, int advance,
+                       int64_t* feedback, int* status_word, void* stream);
+
+/*
+ * ids_out[b] = a draw from softmax(logits[b, :] / temperature) restricted to the top_k largest logits of the row
+ * (top_k = 0: all V columns; logits tied with the top_k-th largest all stay in).  logits [B, V] of `dtype`, row
+ * pitch ld; temperature > 0.  The draw is the Gumbel-max form, argmax_j(logit_j / temperature - log(-log(u_j))),
+ * lowest j on ties, with u_j in (0, 1) a counter-based function of (seed, *step_dev, b, j) (step_dev: device
+ * int32*, NULL = 0), so that a (seed, step) pair always gives the same ids.  Greedy decoding needs no call: the
+ * lm_head GEMM returns the row argmax (b200_gemm_argmax / b200_gemm_rowstats).
+ */
+int b200_sample_logits(const void* logits, int64_t ld, int64_t B, int64_t V, int dtype, float temperature, int top_k, uint64_t seed,
+                       const int32_t* step_dev, int64_t* ids_out, void* stream);
 
 /*
  * Self-test of the bounded waits every tensor-core kernel of this library uses (no reference counterpart): launches

@@ -16,7 +16,10 @@ Triton kernels compute, with the reference's rounding points kept:
 
 Parity is PINNED: ``tests/golden/make_golden.py`` runs the unmodified
 reference under ``TRITON_INTERPRET=1`` and stores its outputs; the CPU test
-suite checks every function here against those vectors.
+suite checks every function here against those vectors.  The exception is the
+"generation" section (``generate_by_recompute``, ``sample_logits``): the
+reference has no inference loop, so those are "parity unpinned" -- defined on
+top of the pinned forward, see the comment there.
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline legs of
 ``bench.py`` may import this module.  The product package never does.
@@ -252,6 +255,64 @@ def lm_head(sd, hidden):
     """The tied head the reference leaves commented out (gpt.py:159-161, 172-179):
     fused_ffn(hidden, wte.T.contiguous(), bias=None)."""
     return fused_ffn(hidden, sd["wte_weight"].T.contiguous())
+
+
+# --------------------------------------------------------------------------- generation (parity unpinned)
+# The reference never built an inference loop (README.md:55 lists "KV cache + sampling" as to do), so nothing below
+# is pinned by reference outputs.  The definition used instead: generating a token means running the reference's
+# whole forward (restated above, pinned) over the sequence so far and picking from the last position's logits; a
+# key/value cache must not change the result beyond rounding.
+@torch.no_grad()
+def generate_by_recompute(sd, cfg, ids, max_new_tokens, pick=None):
+    """ids (batch, prompt_len) -> (tokens (batch, max_new_tokens), last-position logits of every step): every step
+    re-runs gpt_forward + lm_head over the whole sequence; `pick(logits (batch, vocab), position)` chooses the next
+    ids (default: argmax, lowest index on ties)."""
+    seq = ids.clone()
+    tokens, step_logits = [], []
+    for _ in range(max_new_tokens):
+        logits = lm_head(sd, gpt_forward(sd, cfg, seq)[:, -1:, :])[:, 0, :]
+        nxt = logits.float().argmax(dim=-1) if pick is None else pick(logits, seq.shape[1])
+        step_logits.append(logits)
+        tokens.append(nxt)
+        seq = torch.cat([seq, nxt[:, None]], dim=1)
+    return torch.stack(tokens, dim=1), step_logits
+
+
+_M64 = (1 << 64) - 1
+
+
+def _mix64(z: int) -> int:
+    """Finaliser of SplitMix64 (Steele, Lea, Flood 2014) on Python integers, modulo 2^64."""
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return z ^ (z >> 31)
+
+
+def sampling_uniform(seed: int, step: int, row: int, col: int) -> float:
+    """u in (0, 1) of the library's counter-based generator: 23 bits of mix64(mix64(seed + golden * (step + 1)) ^ (row, col))."""
+    key = _mix64((seed + 0x9E3779B97F4A7C15 * ((step & 0xFFFFFFFF) + 1)) & _M64)
+    x = _mix64(key ^ ((row << 32) | col))
+    return ((x >> 41) + 0.5) / 8388608.0
+
+
+def sample_logits(logits, temperature, top_k, seed, step):
+    """Top-k filter + Gumbel-max draw, in float64: returns (ids (rows,), scores (rows, vocab) with -inf where filtered
+    out), scores[r, j] = logits[r, j] / temperature - log(-log(u(seed, step, r, j))).  Columns tied with the k-th
+    largest logit all stay in; the id is the lowest index of the maximum score."""
+    import numpy as np
+
+    x = logits.to(torch.float64).numpy()
+    rows, vocab = x.shape
+    scores = np.full((rows, vocab), -np.inf)
+    for r in range(rows):
+        keep = np.ones(vocab, dtype=bool)
+        if 0 < top_k < vocab:
+            kth = np.sort(x[r])[vocab - top_k]
+            keep = x[r] >= kth
+        u = np.array([sampling_uniform(seed, step, r, j) for j in range(vocab)])
+        sc = x[r] / temperature - np.log(-np.log(u))
+        scores[r, keep] = sc[keep]
+    return torch.from_numpy(scores.argmax(axis=1)), torch.from_numpy(scores)
 
 
 # --------------------------------------------------------------------------- accounting

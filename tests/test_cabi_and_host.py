@@ -32,7 +32,7 @@ def test_library_builds_and_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/b200_gpt.h but not exported"
     assert sorted(_lib.SIGNATURES) == names, "ctypes signature table and header disagree"
     bound = _lib.load()
-    assert bound.b200_abi_version() == 5
+    assert bound.b200_abi_version() == 6
     assert bound.b200_status_string(0) == b"ok"
     assert bound.b200_status_string(6) == b"a kernel abandoned a bounded wait"
 
@@ -80,6 +80,20 @@ def test_argument_checks_need_no_gpu():
     assert lib.b200_gemm_rowstats(one, one, None, 4, 4, 8, 8, 8, 1, 0, None, one, None, None, None, 0, None, None) == 4  # fp32 rounding: unsupported
     assert lib.b200_gemm_rowstats(one, one, None, 4, 4, 8, 8, 8, 1, 1, None, one, None, None, None, 0, None, None) == 5  # no workspace
     assert lib.b200_gemm_rowstats(one, one, None, 0, 4, 8, 8, 8, 1, 1, None, one, None, None, None, 0, None, None) == 0  # M = 0
+    # token-by-token generation: the position lives in device memory and is mandatory; sizes are checked first
+    assert lib.b200_embedding_at(one, one, one, one, 2, 1, 10, 8, 4, 1, None, 1e-5, None, None, None, None) == 1  # no position
+    assert lib.b200_embedding_at(one, one, one, one, 2, 9, 10, 8, 4, 1, None, 1e-5, None, None, one, None) == 1  # L > P
+    assert lib.b200_embedding_at(one, one, one, one, 0, 1, 10, 8, 4, 1, None, 1e-5, None, None, one, None) == 0  # empty batch
+    assert lib.b200_kv_cache_fill(one, one, 2, 9, 64, 8, 1, None) == 1  # more positions than the cache holds
+    assert lib.b200_kv_cache_fill(one, one, 0, 9, 64, 16, 1, None) == 0
+    assert lib.b200_attention_decode(one, one, one, 2, 4, 48, 16, 1.0, 1, one, None, None) == 4  # head size not built
+    assert lib.b200_attention_decode(one, one, one, 2, 4, 64, 16, 1.0, 1, None, None, None) == 1  # no position
+    assert lib.b200_attention_decode(one, one, one, 0, 4, 64, 16, 1.0, 1, one, None, None) == 0
+    assert lib.b200_decode_append(one, one, 4, 8, 2, one, 1, None, None, None) == 1  # row pitch below the column count
+    assert lib.b200_decode_append(one, one, 8, 8, 2, None, 1, None, None, None) == 1
+    assert lib.b200_sample_logits(one, 16, 2, 16, 1, 0.0, 0, 0, None, one, None) == 1  # temperature must be positive
+    assert lib.b200_sample_logits(one, 8, 2, 16, 1, 1.0, 0, 0, None, one, None) == 1  # row pitch below the vocabulary
+    assert lib.b200_sample_logits(one, 16, 0, 16, 1, 1.0, 0, 0, None, one, None) == 0
 
 
 def test_operators_refuse_cpu_tensors():
@@ -149,3 +163,18 @@ def test_huggingface_state_dict_conversion():
     assert torch.equal(model.blocks[0][0].c_attn_bias, hf.h[0].attn.c_attn.bias)
     hf_cfg.n_ctx = 64
     assert convert_huggingface_to_triton(hf.state_dict(), hf_cfg)[1].block_size == 64
+
+
+def test_convert_hf_and_load_model_reads_a_checkpoint_directory(tmp_path):
+    """convert_hf_and_load_model (gpt.py:240-247 of the reference) with a save_pretrained directory in place of
+    the hub id: returns (FusedGPT, GPT2Model), both in eval mode, parameters equal tensor for tensor."""
+    from transformers import GPT2Config, GPT2Model
+
+    from gpt_triton_b200.gpt import convert_hf_and_load_model
+
+    GPT2Model(GPT2Config(vocab_size=512, n_positions=64, n_embd=64, n_layer=2, n_head=2)).save_pretrained(str(tmp_path))
+    model, hf = convert_hf_and_load_model(str(tmp_path), "cpu")
+    assert not model.training and not hf.training
+    assert (model.config.vocab_size, model.config.block_size, model.config.n_layer) == (512, 64, 2)
+    assert torch.equal(model.wte_weight, hf.wte.weight) and torch.equal(model.layer_norm_bias, hf.ln_f.bias)
+    assert torch.equal(model.blocks[1][0].c_proj_weight, hf.h[1].attn.c_proj.weight)

@@ -310,6 +310,29 @@ def test_converted_huggingface_model_matches_transformers(dtype, atol):
     assert (logits - ref_logits).abs().max().item() < atol
 
 
+def test_convert_hf_and_load_model_from_a_checkpoint_directory(tmp_path):
+    """convert_hf_and_load_model (gpt.py:240-247 of the reference) end to end, the way test.py:120-133 uses it,
+    with a checkpoint directory written by save_pretrained standing in for the hub id "gpt2" (GPT-2-small width and
+    head count, 2 layers, seeded): both returned models run on the GPU and their hidden states are compared at
+    the reference's own tolerance (atol 1e-1) and at the tighter bound this engine meets."""
+    from transformers import GPT2Config, GPT2Model
+
+    from gpt_triton_b200.gpt import convert_hf_and_load_model
+
+    torch.manual_seed(5)
+    hf_cfg = GPT2Config(vocab_size=2048, n_positions=256, n_embd=768, n_layer=2, n_head=12,
+                        resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    GPT2Model(hf_cfg).save_pretrained(str(tmp_path))
+    model, hf_model = convert_hf_and_load_model(str(tmp_path), DEV)
+    assert model.config.n_embd == 768 and model.config.block_size == 256 and not model.training
+    ids = torch.randint(0, 2048, (4, 200), generator=torch.Generator().manual_seed(6)).to(DEV)
+    with torch.no_grad():
+        ref = hf_model(ids).last_hidden_state
+    hidden = model(ids)
+    assert torch.allclose(hidden, ref, atol=1e-1)  # the reference's assertion
+    assert (hidden - ref).abs().max().item() < 5e-3
+
+
 def test_training_mode_rejected():
     model, _, _ = build_model(TINY, torch.float32)
     model.train()
