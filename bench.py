@@ -601,13 +601,38 @@ def run_sweep(args):
             del qkv, q, k, v
 
 
+def kernel_trace(replay):
+    """Kernel start/end records (torch.profiler's CUPTI activity records: no counters, nothing is serialised) of one
+    call of `replay`, summed per kernel name, with the idle time between consecutive kernels."""
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        replay()
+        torch.cuda.synchronize()
+    recs = sorted(((ev.time_range.start, ev.time_range.end, ev.name) for ev in prof.events()
+                   if ev.device_type == torch.autograd.DeviceType.CUDA and ev.time_range.end > ev.time_range.start), key=lambda r: r[0])
+    span = recs[-1][1] - recs[0][0]
+    busy = sum(r[1] - r[0] for r in recs)
+    gaps = [(b[0] - a[1], a[2][:60], b[2][:60]) for a, b in zip(recs, recs[1:])]
+    by_name = {}
+    for st, en, name in recs:
+        key = name.split("(")[0][:90]
+        n, t = by_name.get(key, (0, 0.0))
+        by_name[key] = (n + 1, t + (en - st))
+    return {
+        "kernels": len(recs), "span_ms": span / 1e3, "sum_of_kernel_durations_ms": busy / 1e3,
+        "idle_between_kernels_ms": sum(g[0] for g in gaps if g[0] > 0) / 1e3, "overlap_ms": -sum(g[0] for g in gaps if g[0] < 0) / 1e3,
+        "median_gap_us": statistics.median(g[0] for g in gaps),
+        "per_kernel": {k: {"launches": n, "total_ms": t / 1e3} for k, (n, t) in sorted(by_name.items(), key=lambda kv: -kv[1][1])},
+        "largest_gaps_us": [{"gap_us": g[0], "after": g[1], "before": g[2]} for g in sorted(gaps, key=lambda g: -g[0])[:5]],
+    }
+
+
 def run_gap_table(args):
     """Where one replayed forward spends its time between kernels: kernel start/end records of ONE CUDA-graph replay
     of the headline forward (torch.profiler's CUPTI activity records: no counters, no kernel is serialised or
     replayed), summed per kernel name, with the idle time between consecutive kernels (negative when programmatic
     dependent launch lets a kernel's set-up start under its predecessor's tail).  A diagnosis, not a benchmark value."""
-    from torch.profiler import ProfilerActivity, profile
-
     from gpt_triton_b200.gpt import FusedGPT, GPTConfig, GraphedForward
 
     dev = torch.device("cuda", 0)
@@ -629,27 +654,10 @@ def run_gap_table(args):
     e.record()
     torch.cuda.synchronize()
     plain_ms = s.elapsed_time(e) / 10
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        fwd.graph.replay()
-        torch.cuda.synchronize()
-    recs = sorted(((ev.time_range.start, ev.time_range.end, ev.name) for ev in prof.events()
-                   if ev.device_type == torch.autograd.DeviceType.CUDA and ev.time_range.end > ev.time_range.start), key=lambda r: r[0])
-    span = recs[-1][1] - recs[0][0]
-    busy = sum(r[1] - r[0] for r in recs)
-    gaps = [(b[0] - a[1], a[2][:60], b[2][:60]) for a, b in zip(recs, recs[1:])]
-    by_name = {}
-    for st, en, name in recs:
-        key = name.split("(")[0][:90]
-        n, t = by_name.get(key, (0, 0.0))
-        by_name[key] = (n + 1, t + (en - st))
-    print(json.dumps({
-        "what": "one CUDA-graph replay of the forward + lm_head under CUPTI activity tracing", "batch": batch, "seq_len": SEQ,
-        "kernels": len(recs), "span_ms": span / 1e3, "sum_of_kernel_durations_ms": busy / 1e3,
-        "idle_between_kernels_ms": sum(g[0] for g in gaps if g[0] > 0) / 1e3, "overlap_ms": -sum(g[0] for g in gaps if g[0] < 0) / 1e3,
-        "median_gap_us": statistics.median(g[0] for g in gaps), "replay_ms_without_profiler": plain_ms,
-        "per_kernel": {k: {"launches": n, "total_ms": t / 1e3} for k, (n, t) in sorted(by_name.items(), key=lambda kv: -kv[1][1])},
-        "largest_gaps_us": [{"gap_us": g[0], "after": g[1], "before": g[2]} for g in sorted(gaps, key=lambda g: -g[0])[:5]],
-    }))
+    rec = kernel_trace(fwd.graph.replay)
+    rec.update({"what": "one CUDA-graph replay of the forward + lm_head under CUPTI activity tracing", "batch": batch, "seq_len": SEQ,
+                "replay_ms_without_profiler": plain_ms})
+    print(json.dumps(rec))
 
 
 def run_other_model(args):
@@ -688,6 +696,85 @@ def run_other_model(args):
                       "tokens_per_s": batch * seq / (ms * 1e-3), "flop_per_step": flops, "mfu_of_spec_2250": flops / (ms * 1e-3) / 2250e12}))
 
 
+def run_decode(args):
+    """Token-by-token generation of the 124M model (fp16, 512 sequences, 300-token prompts, `--new-tokens` generated
+    greedily, one GPU): time of the prompt pass and of the replayed decode steps, and the HBM roofline of a decode
+    step.  Extra figure for the record (the reference has no inference loop), not the headline metric.
+
+    Algorithmic bytes of one decode step with n tokens already cached: every weight once (the 12 blocks + the tied
+    embedding matrix as lm_head operand + the final LayerNorm) + keys and values of n positions read and of one
+    position written per layer and sequence; activations of 512 rows are noise beside them."""
+    from gpt_triton_b200 import kernels as K
+    from gpt_triton_b200.gpt import FusedGPT, GenerationSession, GPTConfig
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, peak_src = load_peaks()
+    cfg, sd = make_state_dict(torch.float16)
+    model = FusedGPT(GPTConfig(**GPT2_SMALL))
+    model.load_state_dict(sd)
+    model = model.to(torch.float16).to(dev).eval()
+    B, L0, new = args.global_batch, SEQ, args.new_tokens
+    prompt = make_ids(B, 0).to(dev)
+    sess = GenerationSession(model, B, capacity=L0 + new - 1, max_new_tokens=new)
+    tokens = sess.generate(prompt, new)  # prompt pass, two eager steps, capture, replays
+    assert sess.graph is not None
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(args.steps, 3)
+    # the prompt pass (forward + cache fill + first token), eager launches
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(reps):
+        model._body(prompt, kv_caches=sess.kv)
+    e.record()
+    torch.cuda.synchronize()
+    prefill_ms = s.elapsed_time(e) / reps
+    # the decode steps: rewind the device-side position to the end of the prompt (and the id that the first step
+    # embeds to the first generated token) and replay the captured step
+    def rewind():
+        sess.pos.copy_(torch.tensor([L0, L0], dtype=torch.int32))
+        sess.feedback.copy_(tokens[:, 0])
+        torch.cuda.synchronize()
+
+    rewind()
+    lib = K._lib.load()
+    n0 = lib.b200_launch_count()
+    sess._step()  # one eager step, to count this library's launches
+    launches = lib.b200_launch_count() - n0
+    step_ms = []
+    for _ in range(reps):
+        rewind()
+        s.record()
+        for _ in range(new - 1):
+            sess.graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        step_ms.append(s.elapsed_time(e) / (new - 1))
+    assert K.device_status(dev) == 0
+    assert torch.equal(sess.tokens[:, :new], tokens), "replayed steps must regenerate the same ids"
+    if args.gap_table:  # per-kernel times of ONE replayed decode step (the first after the prompt)
+        rewind()
+        rec = kernel_trace(sess.graph.replay)
+        rec.update({"what": "one CUDA-graph replay of a decode step under CUPTI activity tracing", "batch": B, "cached_positions": L0})
+        print(json.dumps(rec))
+        return
+    ms = sorted(step_ms)[len(step_ms) // 2]
+    h, n_layer, V = GPT2_SMALL["n_embd"], GPT2_SMALL["n_layer"], GPT2_SMALL["vocab_size"]
+    weight_bytes = 2 * (n_layer * 12 * h * h + V * h)
+    mean_cached = L0 + (new - 2) / 2.0  # positions in the cache, averaged over the timed steps
+    kv_bytes = n_layer * B * (mean_cached + 1) * 2 * h * 2
+    alg = weight_bytes + kv_bytes
+    print(json.dumps({
+        "metric": "gpt2_124m_decode_tokens_per_s", "value": B / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "ms_per_decode_step": ms,
+        "prompt_pass_ms": prefill_ms, "dtype": "fp16", "data": "synthetic",
+        "config": {"workload": f"GPT-2 124M greedy generation, {B} sequences, {L0}-token prompts, {new} new tokens, key/value cache, "
+                               "one CUDA-graph replay per token", "launches_per_decode_step": int(launches)},
+        "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": alg / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": peak_src, "traffic": None,
+                     "algorithmic_bytes_per_step": alg, "weights_bytes": weight_bytes, "kv_cache_bytes": kv_bytes},
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -703,7 +790,12 @@ def main():
     ap.add_argument("--global-batch", type=int, default=BATCH,
                     help="sequences in the global batch (default 512, the headline; 64 is what one of 8 GPUs runs)")
     ap.add_argument("--gap-table", action="store_true", help="per-kernel time and idle gaps of one replayed forward (diagnosis)")
+    ap.add_argument("--decode", action="store_true", help="time token-by-token generation (key/value cache) instead of the forward")
+    ap.add_argument("--new-tokens", type=int, default=64, help="--decode: tokens generated per sequence")
     args = ap.parse_args()
+    if args.decode:  # (with --gap-table: the per-kernel trace of one decode step instead of the timing line)
+        run_decode(args)
+        return
     if args.gap_table:
         run_gap_table(args)
         return

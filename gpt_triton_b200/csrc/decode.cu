@@ -8,7 +8,7 @@
 // `pos` = {tokens in the cache, prompt length}), so that the kernels of a decode step can be recorded once in a
 // CUDA graph and replayed for every step.  All of these kernels are HBM-bound gathers and streams:
 //   kv_cache_fill_kernel      cache[b, l, 0:2H] = qkv[b, l, H:3H] after the prompt's forward   (2 x B L 2H bytes)
-//   attention_decode_kernel   appends the new token's k, v and attends its q over the cache    (B (pos+1) 2H bytes read)
+//   attention_decode_kernel   appends the new token's k, v and attends its q over the cache    (B (pos+1) 2H elements read)
 //   sample_rows_kernel        top-k filter + Gumbel-max draw over a row of logits              (passes over B V logits, mostly L2)
 //   decode_append_kernel      tokens[b, column] = next id (also into the buffer the next step embeds); pos += 1
 #include "common.cuh"
@@ -62,24 +62,42 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// One warp per (batch, head).  qkv_new [B, 3H] holds the new token's q | k | v; cache [B, cache_len, 2H] holds k | v of
-// the earlier positions.  The warp appends k, v at position pos, then walks the pos + 1 keys in blocks of 64: lane <->
-// key for the scores (each lane reads whole 2 D-byte key rows), lane <-> output columns for P V (each value row is
-// one coalesced read, P broadcast by shuffles).
-template <typename T, int D>
+// qkv_new [B, 3H] holds the new token's q | k | v; cache [B, cache_len, 2H] holds k | v of the earlier positions.
+// The pos + 1 keys are walked in the reference's blocks of 64 (kernels.py:509).  A PAIR of lanes owns a key: lane
+// 2i takes the first D/2 elements of the key and value rows of keys i, i + 16, i + 32, i + 48 of the block, lane
+// 2i + 1 the second D/2, read as 16-byte vectors, so one warp-wide load covers whole 32-byte sectors of 16 rows;
+// the two halves of a dot product meet in one shuffle.  All loads of a block are independent of each other, so many
+// are in flight per lane.  The softmax reference point of a block is the running maximum over the blocks up
+// to and including it, exactly as in the reference's loop (kernels.py:440-468): P = exp(s - that maximum) is
+// rounded to fp16 before it multiplies V, the denominator sums the unrounded P.  Every lane keeps a private D/2-wide
+// piece of the output row in registers (the rescale factor of a block is the same for all lanes); at the end the
+// 16 pieces of each half are added by a halving exchange (D/2 -> D/32 values per lane in four shuffle rounds) that
+// leaves lane l with output columns (l & 1) * D/2 + (l >> 1) * D/32 + [0, D/32).
+// SPLIT = 1: one warp per (batch, head), four per block, no block-level synchronisation.  SPLIT = 4 (few sequences:
+// not enough warps to fill the GPU): the four warps of a block share one (batch, head) and take the 64-key blocks
+// 4g .. 4g + 3 of a group g side by side; the block maxima of a group go through shared memory (one block-level
+// barrier per group), so that warp w still uses the running maximum over blocks 0 .. 4g + w; the warps' partial
+// rows are merged through shared memory at the end.
+template <typename T, int D, int SPLIT>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const T* __restrict__ qkv_new, T* __restrict__ cache, T* __restrict__ out, int64_t BH, int NH, int64_t cache_len,
                         float scale_log2e, const int* __restrict__ pos_dev, int* status_word) {
   __shared__ float q_s[4][D];
+  __shared__ float part_o[4][D];
+  __shared__ float part_ml[4][2];
+  __shared__ float group_max[2][4];
   constexpr int DPL = D / 32;  // output columns per lane
+  constexpr int DH = D / 2;    // elements of a row per lane of a pair
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t w = (int64_t)blockIdx.x * 4 + warp;
+  const int side = lane & 1, kl = lane >> 1;  // which half of the rows; which of the 16 key slots
+  const int64_t w = SPLIT == 1 ? (int64_t)blockIdx.x * 4 + warp : (int64_t)blockIdx.x;
+  const int part = SPLIT == 1 ? 0 : warp;
   const int pos = pos_dev[0];
   if (pos < 0 || pos >= cache_len) {
     if (threadIdx.x == 0 && status_word) atomicCAS(status_word, 0, kSiteCachePosition);
     return;
   }
-  if (w >= BH) return;
+  if (w >= BH) return;  // (SPLIT = 4: the whole block leaves together)
   const int64_t b = w / NH;
   const int h = (int)(w % NH);
   const int64_t H = (int64_t)NH * D, pitch = 2 * H;
@@ -90,76 +108,145 @@ attention_decode_kernel(const T* __restrict__ qkv_new, T* __restrict__ cache, T*
   T* vc = kc + H;
   for (int i = lane; i < D; i += 32) {
     q_s[warp][i] = dot_operand<T>(to_float(qn[i]));
-    kc[(int64_t)pos * pitch + i] = kn[i];
-    vc[(int64_t)pos * pitch + i] = vn[i];
+    if (part == 0) {
+      kc[(int64_t)pos * pitch + i] = kn[i];
+      vc[(int64_t)pos * pitch + i] = vn[i];
+    }
   }
   __syncwarp();
   // (the new token's own key and value are read from qkv_new below, not back from the cache)
   const int n_keys = pos + 1;
-  float m_run = -INFINITY, l_lane = 0.f;
-  float o[DPL];
+  const int n_groups = (n_keys + 64 * SPLIT - 1) / (64 * SPLIT);
+  float m_run = -INFINITY;  // reference maximum of this warp's latest block
+  float m_all = -INFINITY;  // running maximum over all blocks of the groups done so far
+  float l_lane = 0.f;
+  float o[DH];
 #pragma unroll
-  for (int d = 0; d < DPL; ++d) o[d] = 0.f;
-  for (int k0 = 0; k0 < n_keys; k0 += 64) {
-    float s[2];
+  for (int d = 0; d < DH; ++d) o[d] = 0.f;
+  const float* q_mine = q_s[warp] + side * DH;
+  for (int g = 0; g < n_groups; ++g) {
+    const int k0 = (g * SPLIT + part) * 64;
+    float s[4];
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int key = k0 + half * 32 + lane;
-      s[half] = -INFINITY;
+    for (int j = 0; j < 4; ++j) {
+      const int key = k0 + j * 16 + kl;
+      float a = 0.f;
       if (key < n_keys) {
-        const T* kr = key == pos ? kn : kc + (int64_t)key * pitch;
-        float a = 0.f;
+        const T* kr = (key == pos ? kn : kc + (int64_t)key * pitch) + side * DH;
 #pragma unroll
-        for (int c = 0; c < D; c += 8) {
+        for (int c = 0; c < DH; c += 8) {
           float f[8];
           load8(kr + c, f);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) a = fmaf(q_s[warp][c + i], dot_operand<T>(f[i]), a);
+          for (int i = 0; i < 8; ++i) a = fmaf(q_mine[c + i], dot_operand<T>(f[i]), a);
         }
-        s[half] = a * scale_log2e;  // scores in log2 units
+      }
+      a += __shfl_xor_sync(0xffffffffu, a, 1);                      // the other half of the dot product
+      s[j] = key < n_keys ? a * scale_log2e : -INFINITY;            // score in log2 units
+    }
+    const float bm = warp_max(fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3])));
+    float m_new = fmaxf(m_all, bm);
+    if (SPLIT > 1) {
+      if (lane == 0) group_max[g & 1][warp] = bm;
+      __syncthreads();
+#pragma unroll
+      for (int p2 = 0; p2 < SPLIT; ++p2) {
+        const float other = group_max[g & 1][p2];
+        if (p2 < part) m_new = fmaxf(m_new, other);
+        m_all = fmaxf(m_all, other);
+      }
+    } else {
+      m_all = m_new;
+    }
+    if (bm == -INFINITY) continue;  // no key of this block exists (warp-uniform; SPLIT = 4 only)
+    const float mult = ex2_ftz(m_run - m_new);  // 0 for the warp's first block
+    m_run = m_new;
+    float ph[4], psum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float pj = ex2_ftz(s[j] - m_new);  // 0 for keys beyond the last
+      psum += pj;
+      ph[j] = __half2float(__float2half_rn(pj));
+    }
+    l_lane = fmaf(l_lane, mult, side == 0 ? psum : 0.f);  // (both lanes of a pair hold the same scores: count them once)
+#pragma unroll
+    for (int d = 0; d < DH; ++d) o[d] *= mult;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int key = k0 + j * 16 + kl;
+      if (key < n_keys) {
+        const T* vr = (key == pos ? vn : vc + (int64_t)key * pitch) + side * DH;
+#pragma unroll
+        for (int c = 0; c < DH; c += 8) {
+          float f[8];
+          load8(vr + c, f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[c + i] = fmaf(ph[j], dot_operand<T>(f[i]), o[c + i]);
+        }
       }
     }
-    const float m_new = fmaxf(m_run, warp_max(fmaxf(s[0], s[1])));  // finite: key k0 exists
-    const float mult = ex2_ftz(m_run - m_new);                     // 0 for the first block
-    m_run = m_new;
-    const float p0 = ex2_ftz(s[0] - m_new), p1 = ex2_ftz(s[1] - m_new);  // 0 for keys beyond the last
-    l_lane = l_lane * mult + (p0 + p1);
-    const float ph0 = __half2float(__float2half_rn(p0)), ph1 = __half2float(__float2half_rn(p1));
+  }
+  // add up the lanes' pieces and denominators (all relative to the same maximum m_run)
+  float l_warp = warp_sum(l_lane);
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) o[d] *= mult;
-    const int nk = min(64, n_keys - k0);
-#pragma unroll 4
-    for (int i = 0; i < nk; ++i) {
-      const float pi = __shfl_sync(0xffffffffu, i < 32 ? ph0 : ph1, i & 31);
-      const int key = k0 + i;
-      const Vec<T, DPL> vv = *reinterpret_cast<const Vec<T, DPL>*>((key == pos ? vn : vc + (int64_t)key * pitch) + lane * DPL);
+  for (int n = DH / 2, off = 16; off > 1; n >>= 1, off >>= 1) {
+    const bool upper = (lane & off) != 0;
 #pragma unroll
-      for (int d = 0; d < DPL; ++d) o[d] = fmaf(pi, dot_operand<T>(to_float(vv.v[d])), o[d]);
+    for (int i = 0; i < n; ++i) {
+      const float mine = upper ? o[i + n] : o[i];
+      const float theirs = upper ? o[i] : o[i + n];
+      o[i] = mine + __shfl_xor_sync(0xffffffffu, theirs, off);
     }
   }
-  const float inv = 1.0f / warp_sum(l_lane);
+  const int col0 = side * DH + kl * DPL;  // first of this lane's DPL output columns
+  // o[0 .. DPL) now holds output columns col0 + j of this warp's blocks
+  if (SPLIT > 1) {
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) part_o[warp][col0 + j] = o[j];
+    if (lane == 0) part_ml[warp][0] = m_run, part_ml[warp][1] = l_warp;
+    __syncthreads();
+    if (warp != 0) return;
+    l_warp = 0.f;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) o[j] = 0.f;
+#pragma unroll
+    for (int p2 = 0; p2 < SPLIT; ++p2) {
+      const float mp = part_ml[p2][0];
+      const float f = mp == -INFINITY ? 0.f : ex2_ftz(mp - m_all);  // (m_all is the maximum over every block by now)
+      l_warp = fmaf(part_ml[p2][1], f, l_warp);
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) o[j] = fmaf(part_o[p2][col0 + j], f, o[j]);
+    }
+  }
+  const float inv = 1.0f / l_warp;
   Vec<T, DPL> res;
 #pragma unroll
   for (int d = 0; d < DPL; ++d) res.v[d] = from_float<T>(o[d] * inv);
-  *reinterpret_cast<Vec<T, DPL>*>(out + b * H + (int64_t)h * D + lane * DPL) = res;
+  *reinterpret_cast<Vec<T, DPL>*>(out + b * H + (int64_t)h * D + col0) = res;
+}
+
+template <typename T, int D>
+int attention_decode_sized(const void* qkv_new, void* cache, void* out, int64_t BH, int64_t NH, int64_t cache_len, float sl, const int* pos_dev,
+                           int* status_word, cudaStream_t stream) {
+  // one warp per (batch, head) fills the GPU from about 16 warps per SM on; below that, four warps share one
+  if (BH >= (int64_t)sm_count() * 16)
+    attention_decode_kernel<T, D, 1><<<(unsigned)((BH + 3) / 4), 128, 0, stream>>>((const T*)qkv_new, (T*)cache, (T*)out, BH, (int)NH, cache_len, sl,
+                                                                                    pos_dev, status_word);
+  else
+    attention_decode_kernel<T, D, 4><<<(unsigned)BH, 128, 0, stream>>>((const T*)qkv_new, (T*)cache, (T*)out, BH, (int)NH, cache_len, sl, pos_dev,
+                                                                       status_word);
+  note_launches(1);
+  return status_from_cuda(cudaGetLastError());
 }
 
 template <typename T>
 int attention_decode_typed(const void* qkv_new, void* cache, void* out, int64_t B, int64_t NH, int64_t D, int64_t cache_len, float scale,
                            const int* pos_dev, int* status_word, cudaStream_t stream) {
-  const int64_t BH = B * NH;
-  const dim3 grid((unsigned)((BH + 3) / 4)), block(128);
   const float sl = scale * 1.4426950408889634f;
-  if (D == 32)
-    attention_decode_kernel<T, 32><<<grid, block, 0, stream>>>((const T*)qkv_new, (T*)cache, (T*)out, BH, (int)NH, cache_len, sl, pos_dev, status_word);
-  else if (D == 64)
-    attention_decode_kernel<T, 64><<<grid, block, 0, stream>>>((const T*)qkv_new, (T*)cache, (T*)out, BH, (int)NH, cache_len, sl, pos_dev, status_word);
-  else if (D == 128)
-    attention_decode_kernel<T, 128><<<grid, block, 0, stream>>>((const T*)qkv_new, (T*)cache, (T*)out, BH, (int)NH, cache_len, sl, pos_dev, status_word);
-  else
-    return B200_ERR_UNSUPPORTED;
-  note_launches(1);
-  return status_from_cuda(cudaGetLastError());
+  if (D == 32) return attention_decode_sized<T, 32>(qkv_new, cache, out, B * NH, NH, cache_len, sl, pos_dev, status_word, stream);
+  if (D == 64) return attention_decode_sized<T, 64>(qkv_new, cache, out, B * NH, NH, cache_len, sl, pos_dev, status_word, stream);
+  if (D == 128) return attention_decode_sized<T, 128>(qkv_new, cache, out, B * NH, NH, cache_len, sl, pos_dev, status_word, stream);
+  return B200_ERR_UNSUPPORTED;
 }
 
 // ------------------------------------------------------------------ append + advance
@@ -288,8 +375,8 @@ int launch_kv_cache_fill(const void* qkv, void* cache, int64_t B, int64_t L, int
 int launch_attention_decode(const void* qkv_new, void* cache, void* out, int64_t B, int64_t NH, int64_t D, int64_t cache_len, float scale, int dtype,
                             const int* pos_dev, int* status_word, cudaStream_t stream) {
   if (B == 0 || NH == 0) return B200_OK;
-  // whole key rows are read as 16-byte vectors
-  if (((reinterpret_cast<uintptr_t>(qkv_new) | reinterpret_cast<uintptr_t>(cache)) & 15) || (D * dtype_size(dtype)) % 16) return B200_ERR_ALIGNMENT;
+  // half key rows are read as 16-byte vectors
+  if (((reinterpret_cast<uintptr_t>(qkv_new) | reinterpret_cast<uintptr_t>(cache)) & 15) || (D / 2 * dtype_size(dtype)) % 16) return B200_ERR_ALIGNMENT;
   if (B * NH > 0x7fffffffLL * 4 || NH > 0x7fffffff) return B200_ERR_BAD_ARGUMENT;
   switch (dtype) {
     case B200_F32: return attention_decode_typed<float>(qkv_new, cache, out, B, NH, D, cache_len, scale, pos_dev, status_word, stream);
