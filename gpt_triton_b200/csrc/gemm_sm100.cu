@@ -723,8 +723,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_fence_after();
           const uint64_t da = make_smem_desc(smem_a + stage * C::A_STAGE_BYTES);
           const uint64_t db = make_smem_desc(smem_b + stage * C::B_STAGE_BYTES);
+          // (LN == 1: only the first 8 columns of the extension k-block are non-zero: one 16-wide MMA covers it)
+          const int k_steps = (LN == 1 && kb == num_kb_ab) ? 1 : BK / UMMA_K;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
+            if (k >= k_steps) break;
             // advance 16 elements (32 bytes) along K inside the swizzle row: +2 in 16-byte units
             if constexpr (CTAS == 2)
               umma_f16_pair(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (uint32_t)((kb | k) != 0));
