@@ -79,10 +79,10 @@ __device__ __forceinline__ float warp_max(float v) {
 // barrier per group), so that warp w still uses the running maximum over blocks 0 .. 4g + w; the warps' partial
 // rows are merged through shared memory at the end.
 template <typename T, int D, int SPLIT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128)  // (76 registers at D = 64, six blocks per SM; capping at 64 registers for eight measured 16 % slower)
 attention_decode_kernel(const T* __restrict__ qkv_new, T* __restrict__ cache, T* __restrict__ out, int64_t BH, int NH, int64_t cache_len,
                         float scale_log2e, const int* __restrict__ pos_dev, int* status_word) {
-  __shared__ float q_s[4][D];
+  __shared__ __align__(16) float q_s[4][D + 4];  // the second half of q sits 4 floats further on: the two lanes of a pair read different banks
   __shared__ float part_o[4][D];
   __shared__ float part_ml[4][2];
   __shared__ float group_max[2][4];
@@ -107,7 +107,7 @@ attention_decode_kernel(const T* __restrict__ qkv_new, T* __restrict__ cache, T*
   T* kc = cache + b * cache_len * pitch + (int64_t)h * D;
   T* vc = kc + H;
   for (int i = lane; i < D; i += 32) {
-    q_s[warp][i] = dot_operand<T>(to_float(qn[i]));
+    q_s[warp][i + (i >= D / 2 ? 4 : 0)] = dot_operand<T>(to_float(qn[i]));
     if (part == 0) {
       kc[(int64_t)pos * pitch + i] = kn[i];
       vc[(int64_t)pos * pitch + i] = vn[i];
@@ -123,7 +123,7 @@ attention_decode_kernel(const T* __restrict__ qkv_new, T* __restrict__ cache, T*
   float o[DH];
 #pragma unroll
   for (int d = 0; d < DH; ++d) o[d] = 0.f;
-  const float* q_mine = q_s[warp] + side * DH;
+  const float* q_mine = q_s[warp] + side * (DH + 4);
   for (int g = 0; g < n_groups; ++g) {
     const int k0 = (g * SPLIT + part) * 64;
     float s[4];
