@@ -498,6 +498,11 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], const 
     if (col0 + j < N) {
       float v = f[j];
       if (rrow) v += to_float(rrow[j]);
+      if constexpr (LN == 2) {  // (reached by the narrow-tile kernel's ragged last chunk only)
+        if (mom.n == 0.f) mom.shift = v;
+        const float d = v - mom.shift;
+        mom.s1 += d, mom.s2 = fmaf(d, d, mom.s2), mom.n += 1.f;
+      }
       const OutT o = from_float<OutT>(v);
       orow[j] = o;
       f[j] = to_float(o);
@@ -932,6 +937,173 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+
+// ------------------------------------------------------------------ narrow-tile variant for few rows
+// With M <= kNarrowMaxRows (one generated token per sequence; tiny configurations) the 256 x 256 tiles of the kernel
+// above leave most of the GPU idle: a 512 x 768 x 3072 product is 6 tiles, each a serial loop of 48 k-blocks.  This
+// kernel computes ONE 128 x 64 tile per CTA (grid = column tiles x row tiles, no persistence, one accumulator), so
+// the same product becomes 48 CTAs: the same TMA ring, tcgen05.mma (M = 128, N = 64, cta_group::1) and fused
+// epilogue arithmetic (epilogue_chunk, direct 16-byte stores), k-blocks in the same order, hence the same bits.
+// 16-bit output, no row statistics of the argmax kind; LN = 1 / 2 as above, the moments of LN = 2 per 64-column slice.
+// Warp 0: TMA producer; warp 1: tensor-memory owner and MMA issuer; warps 2-5: epilogue (one row per thread).
+constexpr int NARROW_BN = 64;
+constexpr int NARROW_STAGES = 6;
+constexpr int NARROW_A_BYTES = BM * BK * 2;         // 16 KB
+constexpr int NARROW_B_BYTES = NARROW_BN * BK * 2;  // 8 KB
+constexpr int NARROW_STAGE_BYTES = NARROW_A_BYTES + NARROW_B_BYTES;
+constexpr int NARROW_THREADS = 192;
+constexpr int NARROW_CTRL_BYTES = 256;
+constexpr int NARROW_SMEM_BYTES = NARROW_STAGES * NARROW_STAGE_BYTES + 1024 + NARROW_CTRL_BYTES + NARROW_BN * 4;
+constexpr int kNarrowMaxRows = 512;
+
+template <typename OutT, bool GELU, int LN>
+__global__ void __launch_bounds__(NARROW_THREADS, 1)
+gemm_narrow_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_a_ext, const __grid_constant__ CUtensorMap map_b_ext, EpilogueArgs<OutT> epi,
+                   int64_t M, int64_t N, int64_t K, uint32_t idesc, int* status_word) {
+  static_assert(sizeof(OutT) == 2, "the narrow-tile kernel stores 16-bit outputs");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte-swizzled tiles need 1024-byte aligned bases
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = base + NARROW_STAGES * NARROW_A_BYTES;
+  uint8_t* ctrl = smem + NARROW_STAGES * NARROW_STAGE_BYTES;
+  const uint32_t bars = smem_u32(ctrl);
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * NARROW_STAGES, bar_acc = bars + 16 * NARROW_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 16 * NARROW_STAGES + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 16 * NARROW_STAGES + 16);
+  static_assert(16 * NARROW_STAGES + 24 <= NARROW_CTRL_BYTES, "control block too small");
+  float* bias_s = reinterpret_cast<float*>(ctrl + NARROW_CTRL_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * NARROW_BN, m0 = blockIdx.y * BM;
+  const int num_kb_ab = (int)((K + BK - 1) / BK);
+  const int num_kb = num_kb_ab + (LN == 1 ? 1 : 0);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NARROW_STAGES; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, 1);
+    }
+    mbar_init(bar_acc, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), NARROW_BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, status_word, 31)) break;
+        const bool ext = LN == 1 && kb == num_kb_ab;
+        mbar_arrive_expect_tx(bar_full + 8 * stage, NARROW_STAGE_BYTES);
+        tma_load_2d(smem_a + stage * NARROW_A_BYTES, ext ? &map_a_ext : &map_a, bar_full + 8 * stage, ext ? 0 : kb * BK, m0);
+        tma_load_2d(smem_b + stage * NARROW_B_BYTES, ext ? &map_b_ext : &map_b, bar_full + 8 * stage, ext ? 0 : kb * BK, n0);
+        if (++stage == NARROW_STAGES) stage = 0, phase ^= 1u;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, status_word, 32)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const uint64_t da = make_smem_desc(smem_a + stage * NARROW_A_BYTES);
+        const uint64_t db = make_smem_desc(smem_b + stage * NARROW_B_BYTES);
+        const int k_steps = (LN == 1 && kb == num_kb_ab) ? 1 : BK / UMMA_K;  // (the extension block: 8 non-zero columns)
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          if (k >= k_steps) break;
+          umma_f16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (uint32_t)((kb | k) != 0));
+        }
+        umma_commit(bar_empty + 8 * stage);
+        if (++stage == NARROW_STAGES) stage = 0, phase ^= 1u;
+      }
+      if (alive) umma_commit(bar_acc);
+    }
+  } else {
+    // epilogue: warp w reads tensor-memory lanes [32 * (w % 4), + 32) = rows of the tile
+    const int quarter = warp & 3;
+    const int64_t row = (int64_t)m0 + quarter * 32 + lane;
+    const bool row_ok = row < M;
+    const int epi_tid = threadIdx.x - 64;
+    if (epi_tid < NARROW_BN) {
+      const int c = n0 + epi_tid;
+      bias_s[epi_tid] = (LN != 1 && epi.bias && c < N) ? to_float(epi.bias[c]) : 0.f;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+    float ln_r = 1.f;
+    if constexpr (LN == 1) {
+      if (row_ok) ln_r = __ldg(epi.ln_stats + row).y;
+    }
+    const uintptr_t out_al = reinterpret_cast<uintptr_t>(epi.out) | (uintptr_t)(epi.ld_out * 2);
+    const uintptr_t res_al = epi.residual ? (reinterpret_cast<uintptr_t>(epi.residual) | (uintptr_t)(epi.ld_res * 2)) : 0;
+    const int mode = ((out_al | res_al) & 15) == 0 ? STORE_16B : STORE_SCALAR;
+    // residual of this thread's row, fetched while the main loop runs
+    uint4 res[NARROW_BN / 8];
+    const bool res_in_regs = epi.residual && mode != STORE_SCALAR && row_ok;
+    if (res_in_regs) {
+      const OutT* rrow = epi.residual + row * epi.ld_res + n0;
+#pragma unroll
+      for (int i = 0; i < NARROW_BN / 8; ++i)
+        if (n0 + (i / 4) * 32 + 32 <= N) res[i] = *reinterpret_cast<const uint4*>(rrow + i * 8);
+    }
+    if (mbar_wait(bar_acc, 0, abort_flag, status_word, 33)) {
+      tc_fence_after();
+      RowStats unused{-INFINITY, 0, 0.f, -1};
+      SliceMoments mom{0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < NARROW_BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= N) break;  // (warp-uniform)
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+        tmem_ld_wait();
+        if (row_ok)
+          epilogue_chunk<OutT, GELU, 0, LN>(v, bias_s + c * 32, epi, (res_in_regs && col0 + 32 <= N) ? &res[c * 4] : nullptr, row, col0, N, mode, 0u,
+                                            c & 1, lane, row_ok, false, unused, ln_r, mom);
+      }
+      if constexpr (LN == 2) {
+        if (row_ok && mom.n > 0.f) {
+          const float inv = 1.0f / mom.n;
+          epi.stats_out[(int64_t)blockIdx.x * epi.stats_out_ld + row] = make_float2(fmaf(mom.s1, inv, mom.shift), fmaxf(mom.s2 - mom.s1 * mom.s1 * inv, 0.f));
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_d, NARROW_BN);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 // 2-D map over a row-major [rows, cols] 16-bit matrix with leading dimension ld; box = 64 columns x box_rows.
 static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows, int op_dtype) {
@@ -1002,12 +1174,58 @@ struct LnArgs {
   int64_t stats_out_ld = 0;
 };
 
+
+// kind::f16 instruction descriptor of the narrow-tile kernel: M = 128, N = 64.
+static constexpr uint32_t make_idesc_narrow(int ab_format) {
+  return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)(NARROW_BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <typename OutT, bool GELU, int LN>
+static int launch_narrow(const void* a, const void* b, const EpilogueArgs<OutT>& epi, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                         int op_dtype, const LnArgs& ln, int* status_word, cudaStream_t stream) {
+  if constexpr (sizeof(OutT) != 2) {
+    return B200_ERR_UNSUPPORTED;
+  } else {
+    static std::atomic<bool> attr_set[kMaxDevices];
+    const int slot = device_slot();
+    if (slot < 0) return B200_ERR_CUDA;
+    if (!attr_set[slot].load(std::memory_order_acquire)) {
+      if (cudaFuncSetAttribute(gemm_narrow_kernel<OutT, GELU, LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, NARROW_SMEM_BYTES) != cudaSuccess)
+        return B200_ERR_CUDA;
+      attr_set[slot].store(true, std::memory_order_release);
+    }
+    CUtensorMap ma, mb, mae, mbe;
+    memset(&mae, 0, sizeof(mae));
+    memset(&mbe, 0, sizeof(mbe));
+    int st = make_map(&ma, a, M, K, lda, BM, op_dtype);
+    if (st == B200_OK) st = make_map(&mb, b, N, K, ldb, NARROW_BN, op_dtype);
+    if (st == B200_OK && LN == 1) st = make_map(&mae, ln.a_ext, M, kLnExtCols, kLnExtCols, BM, op_dtype);
+    if (st == B200_OK && LN == 1) st = make_map(&mbe, ln.b_ext, N, kLnExtCols, kLnExtCols, NARROW_BN, op_dtype);
+    if (st != B200_OK) return st;
+    LaunchSetup ls(dim3((unsigned)((N + NARROW_BN - 1) / NARROW_BN), (unsigned)((M + BM - 1) / BM)), dim3(NARROW_THREADS), NARROW_SMEM_BYTES, stream);
+    const cudaError_t e = cudaLaunchKernelEx(&ls.cfg, gemm_narrow_kernel<OutT, GELU, LN>, ma, mb, mae, mbe, epi, M, N, K,
+                                             make_idesc_narrow(op_dtype == B200_BF16 ? 1 : 0), status_word);
+    note_launches(1);
+    return status_from_cuda(e);
+  }
+}
+
+// Whether a product goes to the narrow-tile kernel: few rows, 16-bit output, vector-aligned output and residual.
+template <typename OutT, int STATS>
+static bool takes_narrow_tiles(int64_t M, const void* out, int64_t ld_out, const void* residual, int64_t ld_res) {
+  return STATS == 0 && sizeof(OutT) == 2 && M <= kNarrowMaxRows && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_out % 8 == 0 &&
+         (!residual || ((reinterpret_cast<uintptr_t>(residual) & 15) == 0 && ld_res % 8 == 0));
+}
+
 template <typename OutT, bool GELU, int STATS, int LN = 0>
 static int launch_typed(const void* a, const void* b, const void* bias, const void* residual, void* out, int64_t M, int64_t N, int64_t K,
                         int64_t lda, int64_t ldb, int64_t ld_res, int64_t ld_out, int op_dtype, const ArgmaxPartials& am, int* status_word,
                         cudaStream_t stream, const int64_t* targets = nullptr, float* target_val = nullptr, const LnArgs& ln = LnArgs()) {
   EpilogueArgs<OutT> epi{(const OutT*)bias, (const OutT*)residual, (OutT*)out, ld_res, ld_out, 0, am.val, am.idx, am.sum, am.ld, targets, target_val, 0,
                          ln.stats, ln.stats_out, ln.stats_out_ld};
+  if constexpr (STATS == 0) {
+    if (takes_narrow_tiles<OutT, STATS>(M, out, ld_out, residual, ld_res)) return launch_narrow<OutT, GELU, LN>(a, b, epi, M, N, K, lda, ldb, op_dtype, ln, status_word, stream);
+  }
   CUtensorMap mo, mr;
   memset(&mo, 0, sizeof(mo));
   memset(&mr, 0, sizeof(mr));
@@ -1173,7 +1391,7 @@ ln_stats_from_moments_kernel(const float2* __restrict__ moments, int64_t ld, int
 
 size_t gemm_ln_workspace_bytes(int64_t M, int64_t N) {
   if (M <= 0 || N <= 0) return 0;
-  const int64_t slices = (N + gemm::EPI_COLS - 1) / gemm::EPI_COLS;
+  const int64_t slices = (N + gemm::NARROW_BN - 1) / gemm::NARROW_BN;  // (the narrow-tile kernel's slices; the wide kernel uses every other one)
   return (size_t)(slices * ((M + 63) / 64 * 64)) * 8;
 }
 
@@ -1225,14 +1443,19 @@ int launch_gemm_ln(const void* a, const void* b, const void* bias, const void* r
   else B200_GEMM_LN_DISPATCH(__nv_bfloat16);
 #undef B200_GEMM_LN_DISPATCH
   if (st != B200_OK || !stats_out) return st;
-  const int slices = (int)((N + EPI_COLS - 1) / EPI_COLS);
+  // width of the column slices whose moments the GEMM left: the wide kernel's epilogue warps cover EPI_COLS columns, a
+  // narrow tile NARROW_BN
+  const bool narrow = io_dtype == B200_F16 ? takes_narrow_tiles<__half, 0>(M, out, ld_out, residual, ld_res)
+                                           : takes_narrow_tiles<__nv_bfloat16, 0>(M, out, ld_out, residual, ld_res);
+  const int slice_cols = narrow ? NARROW_BN : EPI_COLS;
+  const int slices = (int)((N + slice_cols - 1) / slice_cols);
   LaunchSetup ls(dim3((unsigned)((M + 255) / 256)), dim3(256), 0, stream);
   const cudaError_t e =
       io_dtype == B200_F16
-          ? cudaLaunchKernelEx(&ls.cfg, ln_stats_from_moments_kernel<__half>, (const float2*)ln.stats_out, ln.stats_out_ld, slices, (int)EPI_COLS,
+          ? cudaLaunchKernelEx(&ls.cfg, ln_stats_from_moments_kernel<__half>, (const float2*)ln.stats_out, ln.stats_out_ld, slices, slice_cols,
                                (int)N, eps, M, reinterpret_cast<float2*>(stats_out), static_cast<__half*>(ext_out))
           : cudaLaunchKernelEx(&ls.cfg, ln_stats_from_moments_kernel<__nv_bfloat16>, (const float2*)ln.stats_out, ln.stats_out_ld, slices,
-                               (int)EPI_COLS, (int)N, eps, M, reinterpret_cast<float2*>(stats_out), static_cast<__nv_bfloat16*>(ext_out));
+                               slice_cols, (int)N, eps, M, reinterpret_cast<float2*>(stats_out), static_cast<__nv_bfloat16*>(ext_out));
   note_launches(1);
   return status_from_cuda(e);
 }
