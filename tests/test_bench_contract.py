@@ -67,3 +67,16 @@ def test_gpu_arm_prints_the_contract_line():
     assert d["ms_per_step_x_sm_mhz"] is None or d["ms_per_step_x_sm_mhz"] > 0
     assert set(d["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
     assert "workload" in d["config"] and "l2" in d["config"]
+
+
+@pytest.mark.gpu
+def test_decode_mode_prints_one_line_with_an_hbm_roofline():
+    """`bench.py --decode`: generation with the key/value cache (small batch, few tokens: a functional check of the
+    mode; its own assertions require the replayed decode steps to regenerate the first pass's ids)."""
+    d = run_bench("--decode", "--global-batch", "8", "--new-tokens", "6", "--steps", "3")
+    assert d["metric"] == "gpt2_124m_decode_tokens_per_s" and d["unit"] == "tokens/s" and d["n_gpus"] == 1
+    assert d["value"] > 0 and abs(d["value"] - 8 / (d["ms_per_decode_step"] * 1e-3)) < 1e-3 * d["value"]
+    assert d["config"]["launches_per_decode_step"] == 88  # 1 + 12 x 7 - 1 + final LayerNorm + lm_head + reduce + append
+    r = d["roofline"]
+    assert r["bound"] == "hbm" and r["unit"] == "GB/s" and abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9
+    assert r["algorithmic_bytes_per_step"] == r["weights_bytes"] + r["kv_cache_bytes"]
