@@ -66,7 +66,8 @@ def sharded_forward(fn, ids, gather="argmax", group=None, fn_returns="logits"):
 
     `fn` maps ids to logits (``fn_returns="logits"``, e.g. ``FusedGPT.logits``) or straight to next-token ids
     (``fn_returns="ids"``, e.g. ``FusedGPT.next_ids``, whose argmax comes out of the lm_head's epilogue so that
-    no (tokens, vocab) tensor is written or reduced a second time).
+    no (tokens, vocab) tensor is written or reduced a second time; or ``lambda x: model.generate(x, n)``, whose
+    (rows, n) continuations are gathered the same way).
 
     gather="argmax": (batch, seqlen) int64 next-token ids (8 bytes per token cross NVLink);
     gather="logits": (batch, seqlen, vocab) logits (large: meant for checks, not for throughput);

@@ -2,7 +2,8 @@
 box.  Every rank builds the same seeded GPT-2 (124M shapes, fp16, 3 layers to keep it quick), runs its slice of one
 global batch through `sharding.sharded_forward` over NCCL and checks that the gathered next-token ids are
 bit-identical to the single-GPU `FusedGPT.next_ids` of the whole batch, for an evenly and an unevenly divided
-batch, through the fused-epilogue ids and through materialised logits."""
+batch, through the fused-epilogue ids and through materialised logits; and that a generation (key/value cache)
+split the same way returns the single-GPU continuations."""
 
 import os
 import sys
@@ -44,6 +45,12 @@ def main():
             picked = logits.gather(-1, via_logits[lo:hi, :, None])[..., 0]
             assert torch.equal(picked, logits.max(-1).values), f"rank {rank}: logits-path ids are not row maxima"
             assert torch.equal(logits.gather(-1, whole[lo:hi, :, None])[..., 0], picked)
+        # generation with the key/value cache, batch split over the ranks: the gathered continuations equal the
+        # single-GPU ones (a row's arithmetic does not depend on how many rows share its launch)
+        prompts = torch.randint(0, 50257, (10, 40), generator=torch.Generator().manual_seed(1)).to(dev)
+        whole = model.generate(prompts, 6)
+        got = sharded_forward(lambda x: model.generate(x, 6), prompts, gather="argmax", fn_returns="ids")
+        assert got.shape == whole.shape and torch.equal(got, whole), f"rank {rank}: sharded generation differs"
         assert K.device_status() == 0
         dist.barrier()
         if rank == 0:
