@@ -27,11 +27,13 @@ def _status():
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("D,L", [(64, 1), (64, 2), (64, 64), (64, 65), (64, 300), (32, 129), (128, 70)])
-def test_attention_decode_matches_last_row_of_full_attention(dtype, D, L):
+@pytest.mark.parametrize("D,L,B,NH", [(64, 1, 3, 5), (64, 2, 3, 5), (64, 64, 3, 5), (64, 65, 3, 5), (64, 300, 3, 5), (32, 129, 3, 5), (128, 70, 3, 5),
+                                      # enough (batch, head) pairs for one warp each (the large-batch variant of the kernel)
+                                      (64, 70, 200, 12), (32, 33, 100, 25), (64, 193, 100, 25)])
+def test_attention_decode_matches_last_row_of_full_attention(dtype, D, L, B, NH):
     from gpt_triton_b200 import kernels as K
 
-    B, NH, cap = 3, 5, L + 3
+    cap = L + 3
     H = NH * D
     g = torch.Generator().manual_seed(L * 7 + D)
     q, k, v = (torch.randn((B, NH, L, D), generator=g).to(dtype) for _ in range(3))
@@ -45,7 +47,9 @@ def test_attention_decode_matches_last_row_of_full_attention(dtype, D, L):
     pos = torch.tensor([L - 1, 0], dtype=torch.int32, device=DEV)
     out = K.attention_decode(qkv_new.to(DEV), cache_d, pos, NH).cpu().float()
     assert _status() == 0
-    assert (out - ref).abs().max().item() < TOL[dtype]
+    # (over the 10^5 outputs of the large cases one fp16 rounding of P flips on a last-bit difference of an fp32 score: the
+    # bound on arbitrary inputs is about 5e-4 for any implementation, as for the full attention kernel)
+    assert (out - ref).abs().max().item() < (TOL[dtype] if B * NH < 100 else max(TOL[dtype], 5e-4))
     # the new token's keys and values joined the cache, nothing else was written
     got = cache_d.cpu()
     assert torch.equal(got[:, L - 1], qkv_new[:, H:])
