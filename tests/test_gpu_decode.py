@@ -71,6 +71,28 @@ def test_attention_decode_refuses_a_full_cache():
     assert _status() == 0 and cache[:, cap - 1].eq(1).all()
 
 
+def test_decode_append_columns_feedback_and_overflow():
+    """tokens[:, pos[0] - pos[1] + advance] = ids, the same ids into the feedback buffer, pos[0] += 1 when advancing; a
+    column outside the token buffer writes nothing and is reported through the status word (code 42)."""
+    from gpt_triton_b200 import kernels as K
+
+    B = 700  # more rows than the single block has threads
+    tokens = torch.full((B, 3), -1, dtype=torch.int64, device=DEV)
+    feedback = torch.full((B,), -1, dtype=torch.int64, device=DEV)
+    pos = torch.tensor([9, 9], dtype=torch.int32, device=DEV)
+    ids = [torch.arange(B, device=DEV) * 10 + k for k in range(4)]
+    K.decode_append(ids[0], tokens, pos, advance=False, feedback=feedback)  # the prompt's prediction: column 0, position stays
+    assert pos.tolist() == [9, 9] and torch.equal(tokens[:, 0], ids[0]) and torch.equal(feedback, ids[0]) and (tokens[:, 1:] == -1).all()
+    K.decode_append(ids[1], tokens, pos, advance=True, feedback=feedback)
+    K.decode_append(ids[2], tokens, pos, advance=True)
+    assert pos.tolist() == [11, 9] and torch.equal(tokens[:, 1], ids[1]) and torch.equal(tokens[:, 2], ids[2]) and torch.equal(feedback, ids[1])
+    assert _status() == 0
+    before = tokens.clone()
+    K.decode_append(ids[3], tokens, pos, advance=True, feedback=feedback)  # column 3 does not exist
+    assert _status() == 42
+    assert pos.tolist() == [11, 9] and torch.equal(tokens, before) and torch.equal(feedback, ids[1])
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 def test_kv_cache_fill_copies_keys_and_values(dtype):
     from gpt_triton_b200 import kernels as K
