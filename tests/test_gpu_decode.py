@@ -260,3 +260,25 @@ def test_generation_refuses_what_does_not_fit():
     assert model.generate(prompt, 5).shape == (1, 5)  # positions 0..63
     with pytest.raises(AssertionError):
         model.generate(prompt, 6)
+
+
+def test_generation_at_the_benchmark_size():
+    """GPT-2 124M shapes, fp16, the benchmark's weights and ids: 512 prompts of 300 tokens, 8 tokens generated with the
+    key/value cache (the one-warp-per-head attention variant, the narrow-tile GEMMs at 512 rows, the captured step).
+    Size-independent properties: every generated token is an argmax, to rounding, of the full forward's logits over
+    prompt + tokens at its position; and the continuations of sequences 0, 1, 510, 511 are bit-identical when those
+    four are generated as a batch of their own (rows are independent of their batch)."""
+    from test_gpu_model import GPT2_SMALL
+
+    model, _, _ = build_model(GPT2_SMALL, torch.float16, scale_residual_proj=True)
+    prompt = torch.randint(0, 50257, (512, 300), generator=torch.Generator().manual_seed(0)).to(DEV)
+    new = 8
+    tokens = model.generate(prompt, new)
+    assert tokens.shape == (512, new) and (tokens >= 0).all() and (tokens < 50257).all()
+    seq = torch.cat([prompt, tokens[:, :-1]], dim=1)
+    hidden = model(seq)[:, 299:, :].contiguous()  # positions 299 .. 306 predict tokens 0 .. 7
+    logits = model.lm_head(hidden).float()
+    gap = (logits.max(dim=-1).values - logits.gather(-1, tokens.unsqueeze(-1)).squeeze(-1)).max().item()
+    assert gap <= 2e-2, f"a generated token trails the recomputed argmax by {gap}"
+    sel = torch.tensor([0, 1, 510, 511], device=DEV)
+    assert torch.equal(model.generate(prompt[sel].contiguous(), new), tokens[sel])
